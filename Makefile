@@ -13,10 +13,7 @@ test-gpu:         ## on a B200 box: kernels vs fp32 oracles, models, multi-GPU p
 bench:            ## headline benchmark on 1 GPU (see bench.py for N > 1 under torchrun)
 	$(PY) bench.py
 
-sass:             ## regenerate profiles/sass_summary.md, ptxas_summary.md and the SASS excerpts from the built extension
-	$(PY) scripts/sass_summary.py
-
 harness:          ## standalone tcgen05 GEMM test binaries (no torch)
 	bash tests/cuda/build.sh
 
-.PHONY: build test test-gpu bench sass harness
+.PHONY: build test test-gpu bench harness

@@ -89,7 +89,7 @@ gemm_q_persistent_kernel(const __grid_constant__ CUtensorMap tmap_wq, const __gr
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024 B alignment by *pointer arithmetic* on the __shared__ array: an integer round-trip loses the address space and
-  // turns every LDS/STS below into a generic LD.E/ST.E (checked with cuobjdump -sass)
+  // makes every shared-memory access below a generic one
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* a_ring = smem;                                        // [DQ][D][16 KB]   (1024-aligned)
   uint8_t* ring = a_ring + DQ * D * kATileBytes;                 // [STAGES][STAGE_BYTES]

@@ -46,7 +46,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024B alignment is required by the 128B swizzle atom (8 rows x 128 B)
   // 1024 B alignment by *pointer arithmetic* on the __shared__ array: an integer round-trip loses the address space and
-  // turns every LDS/STS below into a generic LD.E/ST.E (checked with cuobjdump -sass)
+  // makes every shared-memory access below a generic one
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
