@@ -21,7 +21,7 @@ MODEL_REMAPPING = {
     "mistral": "llama",  # reference utils.py:15
 }
 
-SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn", "gusolorn")
+SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn", "gusolorn", "gifetar")
 
 
 @dataclass(frozen=True)
@@ -149,6 +149,8 @@ class ModelConfig:
     layer_specs: Optional[list] = None
     token_side_dim: int = 0
     logit_scale: float = 1.0
+    # gifetar: every sublayer's (normed) output enters the residual stream times this factor
+    residual_mult: float = 1.0
     # quantisation (mlx affine) + sharding
     quantization: Optional[Dict[str, int]] = None
     start_layer: Optional[int] = None
@@ -163,6 +165,8 @@ class ModelConfig:
             d = _perelorn_flat(d)
         elif "model_type" not in d and str(d.get("architecture", "")).lower() == "gusolorn":
             d = _gusolorn_flat(d)
+        elif "model_type" not in d and str(d.get("architecture", "")).lower() == "gifetar":
+            d = _gifetar_flat(d)
         mt = d.get("model_type", "llama")
         if mt == "phi-msft":
             raise ValueError(
@@ -341,6 +345,41 @@ def gusolorn_config(width=2048, vocab=32000, blocks=2, heads=16, ff=8192, expert
         layers += [dict(type="latent_attention", mixer=dict(att), mlp=dict(ff=ff, kind="dense")), ml, ml,
                    dict(type="latent_attention", mixer=dict(att, kv_from=4 * b), mlp=moe)]
     d = dict(architecture="Gusolorn", layers=layers, norm=dict(eps=1e-5), vocab=vocab, width=width)
+    d.update(overrides)
+    return d
+
+
+def _gifetar_flat(d: Dict[str, Any]) -> Dict[str, Any]:
+    """Gifetar's nested config.json (``layers`` = list of {type, mixer, mlp}; ``norm.eps``; ``residual_mult``; ``vocab``; ``width``) -> the
+    flat fields of :class:`ModelConfig`.  Mixer ``attention``: differential attention (heads, kv_heads, dim, vdim, scale, softcap, diff,
+    q_temp.{coef, every}).  Feed-forward: ``moe`` (router.{experts, top}, expert.ff) or none.  Every size is read from the file."""
+    layers = [dict(type=str(L["type"]), mixer=dict(L["mixer"]), mlp=(dict(L["mlp"]) if L.get("mlp") else None)) for L in d["layers"]]
+    for i, L in enumerate(layers):
+        m = L["mixer"]
+        if L["type"] != "attention":
+            raise ValueError(f"Gifetar: unknown mixer type '{L['type']}'")
+        if L["mlp"] is not None and L["mlp"].get("kind") != "moe":
+            raise ValueError(f"Gifetar: unknown feed-forward kind '{L['mlp'].get('kind')}'")
+        if int(m["heads"]) % int(m["kv_heads"]) != 0:
+            raise ValueError(f"Gifetar layer {i}: heads must be a multiple of kv_heads")
+        if L["mlp"] is not None and not (1 <= int(L["mlp"]["router"]["top"]) <= int(L["mlp"]["router"]["experts"])):
+            raise ValueError(f"Gifetar layer {i}: router.top must lie in 1 .. router.experts")
+    out = {k: v for k, v in d.items() if k not in ("architecture", "layers", "norm", "vocab", "width", "residual_mult")}
+    ff = [L["mlp"]["expert"]["ff"] for L in layers if L["mlp"]]
+    out.update(model_type="gifetar", hidden_size=int(d["width"]), vocab_size=int(d["vocab"]), num_hidden_layers=len(layers),
+               rms_norm_eps=float(d["norm"]["eps"]), layer_specs=layers, intermediate_size=int(max(ff)) if ff else 0,
+               residual_mult=float(d.get("residual_mult", 1.0)), tie_word_embeddings=True,
+               num_attention_heads=int(max(L["mixer"]["heads"] for L in layers)))
+    return out
+
+
+def gifetar_config(width=2048, vocab=32000, layers=8, heads=16, kv_heads=4, dim=64, vdim=128, experts=16, top=2, expert_ff=1024,
+                   **overrides) -> Dict[str, Any]:
+    """A Gifetar config.json with layer sizes that resemble a real model: ``layers`` x (differential attention + mixture of experts)."""
+    att = dict(diff=0.8, dim=dim, heads=heads, kv_heads=kv_heads, q_temp=dict(coef=0.1, every=1024), scale=dim ** -0.5, softcap=50.0, vdim=vdim)
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff))
+    d = dict(architecture="Gifetar", layers=[dict(type="attention", mixer=dict(att), mlp=dict(moe)) for _ in range(layers)],
+             norm=dict(eps=1e-5), residual_mult=0.5, vocab=vocab, width=width)
     d.update(overrides)
     return d
 

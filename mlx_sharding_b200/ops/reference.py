@@ -498,7 +498,7 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: Optional[torch.T
 
 
 def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
-    """``act(x @ W^T)`` for any shape / float dtype (fp32 accumulate; ``act``: none | gelu_erf)."""
+    """``act(x @ W^T + W.bias)`` for any shape / float dtype (fp32 accumulate; ``act``: none | gelu_erf)."""
     y = linear(x, W, out_dtype=torch.float32)
     if act == "gelu_erf":
         y = F.gelu(y)
@@ -615,3 +615,108 @@ def moe_clamped_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wg:
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """fp32 router product ``x W^T`` (``w`` fp32 ``[rows, K]``; ``x`` in the activation dtype is widened, never the weight narrowed)."""
     return x.float() @ w.float().t()
+
+
+# ---- layer norms around every sublayer, differential attention over separate key / value pools, top-k softmax router, SiLU-GLU experts
+def layernorm_cast(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``(x - mean) / sqrt(var + eps) * w + b`` (biased variance; fp32 arithmetic) in ``out_dtype``."""
+    xf = x.float()
+    d = xf - xf.mean(-1, keepdim=True)
+    return (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * w.float() + b.float()).to(out_dtype)
+
+
+def post_layernorm_add_norm_(x: torch.Tensor, y: torch.Tensor, post_w: torch.Tensor, post_b: torch.Tensor, mult: float, next_w: torch.Tensor,
+                             next_b: torch.Tensor, eps: float, act_dtype: torch.dtype) -> torch.Tensor:
+    """Sandwich-norm residual step on the fp32 stream ``x`` (in place): ``x += mult * LN(y; post_w, post_b)``, then returns
+    ``LN(x; next_w, next_b)`` in the activation dtype: the input of the sublayer that follows."""
+    x += mult * layernorm_cast(y, post_w, post_b, eps, torch.float32)
+    return layernorm_cast(x, next_w, next_b, eps, act_dtype)
+
+
+def paged_kv_append(rows: torch.Tensor, k_col0: int, v_col0: int, kpool: torch.Tensor, vpool: torch.Tensor, meta: BatchMeta):
+    """Append this step's keys and values to the pools ``[pages, kv_heads, page, d]``: row ``t`` of ``rows`` holds the keys of all heads
+    from column ``k_col0`` on (``kv_heads * d_k`` wide) and the values from ``v_col0`` on; token ``t`` goes to ``meta.slot_mapping[t]``."""
+    P, G, page, dk = kpool.shape
+    dv = vpool.shape[3]
+    slot = meta.slot_mapping.long()
+    pg, off = slot // page, slot % page
+    T = rows.shape[0]
+    kpool[pg, :, off] = rows[:, k_col0:k_col0 + G * dk].reshape(T, G, dk).to(kpool.dtype)
+    vpool[pg, :, off] = rows[:, v_col0:v_col0 + G * dv].reshape(T, G, dv).to(vpool.dtype)
+
+
+def position_temperature(positions: torch.Tensor, coef: float, every: float) -> torch.Tensor:
+    """``1 + coef ln(floor((p + 1) / every) + 1)`` (fp32)."""
+    return 1.0 + coef * torch.log(torch.floor((positions.float() + 1.0) / every) + 1.0)
+
+
+def diff_attention(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, meta: BatchMeta, heads: int, scale: float, softcap: float,
+                   temp_coef: float, temp_every: float, lam: float, eps: float, out_mult: float, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Causal differential attention over paged keys / values.  ``q`` ``[T, >= heads * 2 * d]`` (head by head ``[map 1 | map 2]``), keys
+    ``kpool`` ``[pages, G, page, 2 d]`` laid out the same way, values ``vpool`` ``[pages, G, page, dv]`` shared by both maps; query head ``h``
+    reads key / value head ``h // (heads / G)``.  Per map: ``s = cap tanh(q . k * scale * temp(p) / cap)`` (``softcap == 0``: no cap;
+    ``temp`` = :func:`position_temperature` of the query's position, 1 when ``temp_coef == 0``), softmax over the keys ``j <= p``,
+    ``a = P V``.  Then ``o = a1 - lam * a2``, ``o / sqrt(mean(o^2) + eps) * out_mult`` per head.  Returns ``[T, heads * dv]``."""
+    T = q.shape[0]
+    P, G, page, dk2 = kpool.shape
+    d, dv, rep = dk2 // 2, vpool.shape[3], heads // G
+    qf = q[:, :heads * dk2].float().view(T, heads, 2, d)
+    temp = position_temperature(meta.positions, temp_coef, temp_every) if temp_coef != 0.0 else torch.ones(T, device=q.device)
+    out = torch.empty(T, heads, dv, dtype=torch.float32, device=q.device)
+    bt = meta.block_tables.long()
+    for b, (s, e, c0, _) in enumerate(_seq_ranges(meta)):
+        n = c0 + (e - s)
+        idx = torch.arange(n, device=q.device)
+        pg, off = bt[b, idx // page], idx % page
+        K = kpool[pg, :, off].float().view(n, G, 2, d).repeat_interleave(rep, 1)          # [n, H, 2, d]
+        V = vpool[pg, :, off].float().repeat_interleave(rep, 1)                           # [n, H, dv]
+        sc = torch.einsum("thcd,nhcd->thcn", qf[s:e], K) * (scale * temp[s:e]).view(-1, 1, 1, 1)
+        if softcap:
+            sc = softcap * torch.tanh(sc / softcap)
+        qpos = (c0 + torch.arange(e - s, device=q.device))[:, None]
+        sc = sc.masked_fill((idx[None, :] > qpos)[:, None, None, :], float("-inf"))
+        a = torch.einsum("thcn,nhv->thcv", torch.softmax(sc, -1), V)
+        o = a[:, :, 0] - lam * a[:, :, 1]
+        out[s:e] = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_mult
+    return out.view(T, heads * dv).to(out_dtype)
+
+
+def diff_attention_prefill(q, kpool, vpool, meta: BatchMeta, heads: int, scale: float, softcap: float, temp_coef: float, temp_every: float,
+                           lam: float, eps: float, out_mult: float, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Single-sequence prefill form of :func:`diff_attention` (the CUDA backend runs it as matrix products); same math here."""
+    return diff_attention(q, kpool, vpool, meta, heads, scale, softcap, temp_coef, temp_every, lam, eps, out_mult, out_dtype)
+
+
+def softmax_topk(z: torch.Tensor, bias: Optional[torch.Tensor], num_experts: int, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router on fp32 logits ``z[:, :num_experts] + bias``: the ``top`` largest logits (ties: lowest id), weights = softmax over the chosen
+    logits alone.  Returns ``(idx int32 [T, top], w fp32 [T, top])``."""
+    zz = z[:, :num_experts].float()
+    if bias is not None:
+        zz = zz + bias.float()
+    order = torch.sort(zz, dim=-1, descending=True, stable=True).indices[:, :top]
+    return order.to(torch.int32), torch.softmax(torch.gather(zz, 1, order), -1)
+
+
+def silu_glu(g: torch.Tensor, u: torch.Tensor, out_dtype: torch.dtype, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(g) * u * s`` with ``s`` = ``row_scale`` (per row, default 1): scaling the input of the down projection equals scaling its
+    output."""
+    h = F.silu(g.float()) * u.float()
+    if row_scale is not None:
+        h = h * row_scale.float()[:, None]
+    return h.to(out_dtype)
+
+
+def moe_glu_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight) -> torch.Tensor:
+    """``y[t] = sum_j w[t,j] expert_{idx[t,j]}(x[t])`` with experts ``W_down (silu(W_gate x) * (W_up x))``: the router weight scales the
+    expert's OUTPUT.  Banks ``Wg``, ``Wu`` ``[E, F, K]``, ``Wd`` ``[E, K, F]``.  Returns fp32 ``[T, K]``."""
+    T, k = idx.shape
+    y = torch.zeros(T, Wd.weight.shape[1], dtype=torch.float32, device=x.device)
+    il = idx.long()
+    for e in range(Wg.weight.shape[0]):
+        tok, slot = torch.where(il == e)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok].float()
+        h = silu_glu(xe @ Wg.weight[e].float().t(), xe @ Wu.weight[e].float().t(), x.dtype)
+        y.index_add_(0, tok, (h.float() @ Wd.weight[e].float().t()) * w[tok, slot].float()[:, None])
+    return y

@@ -95,11 +95,11 @@ def key_in_shard(key: str, spec: ShardSpec, tied_embeddings: bool = False, model
     """True if checkpoint tensor ``key`` belongs to stage ``spec`` (half-layer boundaries included)."""
     if "rotary_emb.inv_freq" in key:
         return False
-    if model_type in ("perelorn", "gusolorn"):       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
+    if model_type in ("perelorn", "gusolorn", "gifetar"):       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
         m = re.match(r"l(\d+)\.", key)
         if m:
             return spec.owns_layer(int(m.group(1)))
-        return spec.is_last if key in ("final.norm", "head") else True
+        return spec.is_last if key in ("final.norm", "final.norm.b", "head") else True
     m = _LAYER_RE.match(key)
     if m:
         i = int(m.group(1))
@@ -254,6 +254,9 @@ def random_state_dict(cfg: ModelConfig, spec: Optional[ShardSpec] = None, dtype=
         return
     if cfg.model_type == "gusolorn":
         yield from _gusolorn_random(cfg, gen, dtype, device, seed)
+        return
+    if cfg.model_type == "gifetar":
+        yield from _gifetar_random(cfg, gen, dtype, device, seed)
         return
     H = cfg.hidden_size
     q = quantization
@@ -483,3 +486,37 @@ def write_synthetic_checkpoint(path: str, config: Dict, dtype=torch.bfloat16, se
 
         write_byte_tokenizer(path, vocab_size=cfg.vocab_size)
     return path
+
+
+def _gifetar_random(cfg: ModelConfig, gen, dtype, device, seed: int):
+    """Random-init Gifetar tensors (checkpoint names and shapes of that design: layer norms with weight and bias, attention projections with
+    biases, the four lambda vectors, per-expert matrices, router with bias; the LM head is the embedding table)."""
+    gen.manual_seed(seed * 1000003 + 31)
+    W = cfg.hidden_size
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
+    lin = lambda o, i, gain=1.0: (rn(o, i) * gain / (i ** 0.5)).to(dtype)
+    vec = lambda n: (1.0 + 0.1 * rn(n)).to(dtype)
+    small = lambda n, std=0.2: (std * rn(n)).to(dtype)
+    yield "embed", rn(cfg.vocab_size, W).to(dtype)
+    for i, L in enumerate(cfg.layer_specs):
+        p, m, mlp = f"l{i}.", L["mixer"], L["mlp"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if mlp else ()):
+            yield p + n, vec(W)
+            yield p + n + ".b", small(W)
+        H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        for n, rows in (("q", H * 2 * D), ("k", G * 2 * D), ("v", G * V)):
+            yield p + "mix." + n, lin(rows, W)
+            yield p + "mix." + n + ".b", small(rows)
+        for n in ("lq1", "lk1", "lq2", "lk2"):
+            yield p + "mix." + n, small(D, 0.3)
+        yield p + "mix.o", lin(W, H * V)
+        if mlp:
+            F, E = int(mlp["expert"]["ff"]), int(mlp["router"]["experts"])
+            for e in range(E):
+                yield p + f"mlp.e{e}.gate", lin(F, W, 2.0)
+                yield p + f"mlp.e{e}.up", lin(F, W, 2.0)
+                yield p + f"mlp.e{e}.down", lin(W, F)
+            yield p + "mlp.router", lin(E, W, 3.0)
+            yield p + "mlp.router.b", small(E)
+    yield "final.norm", vec(W)
+    yield "final.norm.b", small(W)
