@@ -195,7 +195,7 @@ class PerelornStage(StageModel):
         """``x``: token ids ``[T]``.  Returns fp32 logits ``[B, V]`` (``[T, V]`` with ``all_logits``).  ``layer_out``: optional list that
         receives a copy of the residual stream after every layer."""
         O, c = self.ops, self.cfg
-        if meta.state_slots is None:
+        if meta.state_slots is None and any(L["type"] in ("mamba2", "lightning") for L in self.specs):      # a stack of attention layers alone holds pages only
             raise ValueError("Perelorn needs state slots in the step metadata (BatchMeta.build(..., state_slots=...))")
         tokens = x.to(torch.int64).contiguous()
         W = c.hidden_size

@@ -492,14 +492,18 @@ def _slots(meta: BatchMeta) -> torch.Tensor:
 
 
 def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
-    """``act(x @ W^T)``.  bf16 operands whose shapes fit the TMA rules (K and N multiples of 8, 16-byte aligned rows) take the tcgen05 GEMM;
-    fp32 operands (exact mode) and odd shapes go to cuBLAS."""
+    """``act(x @ W^T + W.bias)``.  bf16 operands whose shapes fit the TMA rules (K and N multiples of 8, 16-byte aligned rows) take the
+    tcgen05 GEMM (bias in its epilogue); fp32 operands (exact mode) and odd shapes go to cuBLAS."""
     w = W.weight
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] > 0):
-        y = C().linear(x, w, None, None, None, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+        y = C().linear(x, w, None, None, W.bias, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+    elif out_dtype == torch.float32 and x.dtype != torch.float32:
+        # odd shapes with an fp32 result (scores, residual-stream inputs): the library product of the widened operands, so that the
+        # result is not rounded to bf16 on its way out
+        y = torch.nn.functional.linear(x.float(), w.float(), None if W.bias is None else W.bias.float())
     else:
-        y = torch.nn.functional.linear(x, w)
+        y = torch.nn.functional.linear(x, w, W.bias)
         y = y if y.dtype == out_dtype else y.to(out_dtype)
     if act == "gelu_erf":
         return gelu_erf_(y)
@@ -616,6 +620,11 @@ def sigmoid_topk(z, num_experts: int, top: int):
     return idx, w
 
 
+def softmax_topk(z, bias, num_experts: int, top: int):
+    idx, w = C().hy_sigmoid_topk(z, int(num_experts), int(top), 1, bias)
+    return idx, w
+
+
 ACT_CLAMPED_GLU = 3      # two-weight GEMM epilogue: min(g, limit) sigmoid(1.702 .) (clamp(u, +-limit) + 1)
 
 
@@ -639,7 +648,21 @@ def clamped_gated_up(x, Wg: LinearWeight, Wu: LinearWeight, limit: float):
 
 
 def moe_clamped_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight, limit: float):
-    """Routed clamped-GLU experts with the router weight on the expert's input.  bf16 banks whose sizes fit the grouped tcgen05 GEMM
+    return _moe_experts(x, idx, w, Wg, Wu, Wd, float(limit), 0)
+
+
+def moe_glu_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight):
+    """Routed SiLU-GLU experts with the router weight on the expert's OUTPUT (applied in fp32 where the pairs are summed per token); same
+    three paths as :func:`moe_clamped_experts`."""
+    return _moe_experts(x, idx, w, Wg, Wu, Wd, 0.0, 1)
+
+
+def silu_glu(g, u, out_dtype=None, row_scale=None):
+    return C().hy_clamped_glu(g, u, 0.0, None, row_scale, 1)
+
+
+def _moe_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight, limit: float, kind: int):
+    """``kind`` 0: routed clamped-GLU experts with the router weight on the expert's input.  ``kind`` 1: SiLU-GLU experts, weight on the output.  bf16 banks whose sizes fit the grouped tcgen05 GEMM
     (expert rows multiples of 128, inner sizes multiples of 8): counting-sort permutation that scales each gathered row by its pair's
     weight -> grouped two-weight GEMM with the clamped GLU in its epilogue -> grouped down GEMM (fp32) -> sum per token.  Exact mode
     (fp32) and other sizes apply the weight to the gate / up products (linear in the input) and run either one weight-row read per
@@ -649,18 +672,22 @@ def moe_clamped_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: Linea
     wg, wu, wd = Wg.weight, Wu.weight, Wd.weight
     E, F, K = wg.shape
     wflat = w.reshape(-1).contiguous()
+    in_scale, out_wts = (wflat, None) if kind == 0 else (None, wflat)
     if _tc_ok(x) and wg.dtype == torch.bfloat16 and F % 128 == 0 and K % 128 == 0:
-        offs, pair_row, xp = c.moe_permute(idx, x, E, wflat)
-        h = c.grouped_linear(xp, wg, wu, offs, T, ACT_CLAMPED_GLU, False, act_limit=float(limit))
+        offs, pair_row, xp = c.moe_permute(idx, x, E, in_scale)
+        if kind == 0:
+            h = c.grouped_linear(xp, wg, wu, offs, T, ACT_CLAMPED_GLU, False, act_limit=float(limit))
+        else:
+            h = c.grouped_linear(xp, wg, wu, offs, T, ACT_IDS["silu"], False)
         y = c.grouped_linear(h, wd, None, offs, T, 0, True)
-        return c.hy_gather_sum(y, pair_row, int(k))
+        return c.hy_gather_sum(y, pair_row, int(k), out_wts)
     R = T * k
     if R <= PAIR_KERNEL_MAX_ROWS or torch.cuda.is_current_stream_capturing():
         ids = idx.reshape(-1).contiguous()
         h = c.hy_clamped_glu(c.hy_expert_rows_linear(x, int(k), wg, ids, False), c.hy_expert_rows_linear(x, int(k), wu, ids, False),
-                             float(limit), None, wflat)
+                             float(limit), None, in_scale, kind)
         y = c.hy_expert_rows_linear(h, 1, wd, ids, True)
-        return y if k == 1 else y.view(T, k, K).sum(1)
+        return c.hy_gather_sum(y, None, int(k), out_wts)
     flat = idx.reshape(-1).long()
     order = torch.sort(flat, stable=True).indices
     pair_row = torch.empty_like(order, dtype=torch.int32)
@@ -674,14 +701,75 @@ def moe_clamped_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: Linea
             torch.matmul(xp[r0:r0 + n], wg[e].t(), out=g[r0:r0 + n])
             torch.matmul(xp[r0:r0 + n], wu[e].t(), out=u[r0:r0 + n])
         r0 += n
-    h = c.hy_clamped_glu(g, u, float(limit), pair_row, wflat)
+    h = c.hy_clamped_glu(g, u, float(limit), pair_row, in_scale, kind)
     y = torch.empty(R, K, dtype=torch.float32, device=x.device)
     r0 = 0
     for e, n in enumerate(counts):
         if n:
             y[r0:r0 + n] = torch.matmul(h[r0:r0 + n], wd[e].t()).float()
         r0 += n
-    return c.hy_gather_sum(y, pair_row, int(k))
+    return c.hy_gather_sum(y, pair_row, int(k), out_wts)
 
 
 PAIR_KERNEL_MAX_ROWS = 64
+
+
+# ---- sandwich layer norms, separate key / value pools, differential attention (``ops/csrc/diffattn.cu``; same functions as in ``ops/reference.py``)
+def layernorm_cast(x, w, b, eps: float, out_dtype):
+    return C().hy_layernorm_cast(x, w, b, float(eps), _is32(out_dtype))
+
+
+def post_layernorm_add_norm_(x, y, post_w, post_b, mult: float, next_w, next_b, eps: float, act_dtype):
+    return C().hy_post_layernorm_add_norm_(x, y, post_w, post_b, float(mult), next_w, next_b, float(eps), _is32(act_dtype))
+
+
+def paged_kv_append(rows, k_col0: int, v_col0: int, kpool, vpool, meta: BatchMeta):
+    C().hy_paged_kv_append(rows, int(k_col0), int(v_col0), kpool, vpool, meta.slot_mapping)
+
+
+def diff_attention(q, kpool, vpool, meta: BatchMeta, heads: int, scale: float, softcap: float, temp_coef: float, temp_every: float, lam: float,
+                   eps: float, out_mult: float, out_dtype=None):
+    return C().hy_diff_attention(q, kpool, vpool, meta.block_tables, meta.positions, meta.cu_seqlens, int(heads), float(scale), float(softcap),
+                                 float(temp_coef), float(temp_every), float(lam), float(eps), float(out_mult), int(meta.max_ctx_len))
+
+
+def diff_attention_prefill(q, kpool, vpool, meta: BatchMeta, heads: int, scale: float, softcap: float, temp_coef: float, temp_every: float,
+                           lam: float, eps: float, out_mult: float, out_dtype=None):
+    """:func:`diff_attention` for a step that holds ONE sequence with many query rows (a prompt or a portion of one), as matrix products
+    per key / value head ``g`` and map ``c``: gather the sequence's cached keys ``K_gc`` ``[ctx, d]`` and values ``V_g`` from its pages,
+    ``S = Q_gc K_gc^T`` (fp32 out) for the ``heads / G`` query heads of the group at once, the capped, temperature-scaled causal softmax
+    (``hy_sink_softmax``), ``A_gc = P V_g`` (fp32 out); one last kernel takes the difference of the two maps and its per-head norm.  The
+    products run on the tensor cores (tcgen05 GEMM; cuBLAS fp32 in exact mode); query rows go in blocks so that a score matrix stays
+    below 256 MB."""
+    T = q.shape[0]
+    P, G, page, D2 = kpool.shape
+    D, V, Rg = D2 // 2, vpool.shape[3], heads // G
+    ctx = int(meta.max_ctx_len)
+    ctx0, npad = ctx - T, (ctx + 7) // 8 * 8
+    pages = meta.block_tables[0, :(ctx + page - 1) // page].long()
+    is32 = _is32(q.dtype)
+    # [G, ctx (padded with any finite rows: their probability is 0), .] copies of this sequence's keys and values
+    Kc = kpool[pages].permute(1, 0, 2, 3).reshape(G, -1, D2)
+    Vc = vpool[pages].permute(1, 0, 2, 3).reshape(G, -1, V)
+    if Kc.shape[1] < npad:
+        Kc, Vc = torch.nn.functional.pad(Kc, (0, 0, 0, npad - Kc.shape[1])), torch.nn.functional.pad(Vc, (0, 0, 0, npad - Vc.shape[1]))
+    Kc = Kc[:, :npad].reshape(G, npad, 2, D).permute(0, 2, 1, 3).contiguous()             # [G, 2, npad, D]
+    Vt = Vc[:, :npad].transpose(1, 2).contiguous()                                         # [G, V, npad]
+    Q = q[:, :heads * D2].reshape(T, G, Rg, 2, D).permute(1, 3, 0, 2, 4).contiguous()      # [G, 2, T, Rg, D]
+    A = torch.empty(G, 2, T * Rg, V, dtype=torch.float32, device=q.device)
+    block = max(1, (1 << 26) // (npad * Rg))
+    for g in range(G):
+        Wv = LinearWeight(weight=Vt[g])
+        for c in range(2):
+            Wk = LinearWeight(weight=Kc[g, c])
+            for t0 in range(0, T, block):
+                n = min(T, t0 + block) - t0
+                kb = min(npad, (ctx0 + t0 + n + 7) // 8 * 8)          # keys this block of queries can see
+                if kb < npad:
+                    Wk_b, Wv_b = LinearWeight(weight=Kc[g, c, :kb]), LinearWeight(weight=Vt[g, :, :kb].contiguous())
+                else:
+                    Wk_b, Wv_b = Wk, Wv
+                s = linear_any(Q[g, c, t0:t0 + n].reshape(n * Rg, D), Wk_b, torch.float32)
+                p = C().hy_sink_softmax(s, None, int(Rg), int(ctx0 + t0), float(scale), is32, 0, 0, float(softcap), float(temp_coef), float(temp_every))
+                A[g, c, t0 * Rg:(t0 + n) * Rg] = linear_any(p, Wv_b, torch.float32)
+    return C().hy_diff_head_norm(A, int(T), int(heads), float(lam), float(eps), float(out_mult), is32)

@@ -11,6 +11,7 @@
 #include "gemm_tcgen05.h"
 #include "kernels.h"
 #include "hybrid.h"
+#include "diffattn.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -977,7 +978,7 @@ Tensor hy_rotate_half_(Tensor q, const Tensor& positions, const Tensor& inv_freq
 }
 
 Tensor hy_sink_softmax(const Tensor& s, const c10::optional<Tensor>& sink, int64_t H, int64_t ctx0, double scale, bool out_f32, int64_t window,
-                       int64_t k0) {
+                       int64_t k0, double softcap, double temp_coef, double temp_every) {
   check_f32c(s, "scores");
   if (sink.has_value()) check_f32c(*sink, "sink");
   TORCH_CHECK(s.dim() == 2 && (!sink.has_value() || sink->numel() == H) && s.size(0) % H == 0 && window >= 0 && k0 >= 0);
@@ -985,7 +986,8 @@ Tensor hy_sink_softmax(const Tensor& s, const c10::optional<Tensor>& sink, int64
   Tensor out = torch::empty({s.size(0), s.size(1)}, s.options().dtype(act_type(out_f32)));
   if (s.size(0) == 0) return out;
   LAUNCH_OK(b200::sink_softmax_launch(s.data_ptr<float>(), sink.has_value() ? sink->data_ptr<float>() : nullptr, (int)H, (int)s.size(1), (int)ctx0,
-                                      (float)scale, out.data_ptr(), out_f32, (long long)s.size(0), (int)window, (int)k0, cur_stream()));
+                                      (float)scale, out.data_ptr(), out_f32, (long long)s.size(0), (int)window, (int)k0, (float)softcap, (float)temp_coef,
+                                      (float)temp_every, cur_stream()));
   return out;
 }
 
@@ -1030,18 +1032,21 @@ Tensor hy_mlstm_scan(const Tensor& qkv, const Tensor& gates, const Tensor& gate_
   return out;
 }
 
-std::vector<Tensor> hy_sigmoid_topk(const Tensor& z, int64_t E, int64_t top) {
+std::vector<Tensor> hy_sigmoid_topk(const Tensor& z, int64_t E, int64_t top, int64_t mode, const c10::optional<Tensor>& bias) {
   check_rows(z, "z");
-  TORCH_CHECK(z.is_cuda() && z.scalar_type() == torch::kFloat32 && z.dim() == 2 && z.size(1) >= E && top >= 1 && top <= E);
+  TORCH_CHECK(z.is_cuda() && z.scalar_type() == torch::kFloat32 && z.dim() == 2 && z.size(1) >= E && top >= 1 && top <= E && (mode == 0 || mode == 1));
+  if (bias.has_value()) { check_f32c(*bias, "bias"); TORCH_CHECK(bias->numel() >= E && mode == 1); }
   const c10::cuda::CUDAGuard guard(z.device());
   Tensor idx = torch::empty({z.size(0), top}, z.options().dtype(torch::kInt32)), w = torch::empty({z.size(0), top}, z.options());
   if (z.size(0) == 0) return {idx, w};
-  LAUNCH_OK(b200::sigmoid_topk_launch(z.data_ptr<float>(), z.stride(0), (int)E, (int)top, idx.data_ptr<int>(), w.data_ptr<float>(), (int)z.size(0), cur_stream()));
+  LAUNCH_OK(b200::router_topk_launch(z.data_ptr<float>(), z.stride(0), bias.has_value() ? bias->data_ptr<float>() : nullptr, (int)mode, (int)E, (int)top,
+                                     idx.data_ptr<int>(), w.data_ptr<float>(), (int)z.size(0), cur_stream()));
   return {idx, w};
 }
 
 // row_of / scale (both optional, one entry per processed row): block i handles row row_of[i] of g and u with scale[i]
-Tensor hy_clamped_glu(const Tensor& g, const Tensor& u, double limit, const c10::optional<Tensor>& row_of, const c10::optional<Tensor>& scale) {
+Tensor hy_clamped_glu(const Tensor& g, const Tensor& u, double limit, const c10::optional<Tensor>& row_of, const c10::optional<Tensor>& scale,
+                      int64_t kind) {
   check_act(g, "gate"); check_rows(g, "gate"); check_act(u, "up"); check_rows(u, "up");
   TORCH_CHECK(g.dim() == 2 && u.sizes() == g.sizes() && u.scalar_type() == g.scalar_type());
   const int64_t F = g.size(1), rows = row_of.has_value() ? row_of->numel() : g.size(0);
@@ -1052,7 +1057,7 @@ Tensor hy_clamped_glu(const Tensor& g, const Tensor& u, double limit, const c10:
   if (rows == 0) return out;
   LAUNCH_OK(b200::clamped_glu_launch(g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), (int)F, (float)limit,
                                      row_of.has_value() ? row_of->data_ptr<int>() : nullptr, scale.has_value() ? scale->data_ptr<float>() : nullptr,
-                                     out.data_ptr(), is_f32(g), (int)rows, cur_stream()));
+                                     out.data_ptr(), is_f32(g), (int)rows, (int)kind, cur_stream()));
   return out;
 }
 
@@ -1071,14 +1076,104 @@ Tensor hy_expert_rows_linear(const Tensor& x, int64_t div, const Tensor& W, cons
   return out;
 }
 
-Tensor hy_gather_sum(const Tensor& y, const Tensor& row_of, int64_t k) {
-  check_f32c(y, "y"); check_i32(row_of, "row_of");
-  TORCH_CHECK(y.dim() == 2 && k >= 1 && row_of.numel() % k == 0);
+Tensor hy_gather_sum(const Tensor& y, const c10::optional<Tensor>& row_of, int64_t k, const c10::optional<Tensor>& wts) {
+  check_f32c(y, "y");
+  if (row_of.has_value()) check_i32(*row_of, "row_of");
+  const int64_t pairs = row_of.has_value() ? row_of->numel() : y.size(0);
+  TORCH_CHECK(y.dim() == 2 && k >= 1 && pairs % k == 0);
+  if (wts.has_value()) { check_f32c(*wts, "wts"); TORCH_CHECK(wts->numel() == pairs); }
   const c10::cuda::CUDAGuard guard(y.device());
-  const int64_t T = row_of.numel() / k;
+  const int64_t T = pairs / k;
   Tensor out = torch::empty({T, y.size(1)}, y.options());
   if (T == 0) return out;
-  LAUNCH_OK(b200::gather_sum_launch(y.data_ptr<float>(), row_of.data_ptr<int>(), (int)k, (int)y.size(1), out.data_ptr<float>(), (int)T, cur_stream()));
+  LAUNCH_OK(b200::gather_sum_launch(y.data_ptr<float>(), row_of.has_value() ? row_of->data_ptr<int>() : nullptr, wts.has_value() ? wts->data_ptr<float>() : nullptr,
+                                    (int)k, (int)y.size(1), out.data_ptr<float>(), (int)T, cur_stream()));
+  return out;
+}
+
+// ---- sandwich layer norms, key / value append, differential attention (diffattn.cu)
+Tensor hy_layernorm_cast(const Tensor& x, const Tensor& w, const Tensor& b, double eps, bool out_f32) {
+  check_rows(x, "x"); check_f32c(w, "w"); check_f32c(b, "b");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && w.numel() == x.size(1) && b.numel() == x.size(1));
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), x.size(1)}, x.options().dtype(act_type(out_f32)));
+  if (x.size(0) == 0) return out;
+  LAUNCH_OK(b200::layernorm_cast_launch(x.data_ptr<float>(), x.stride(0), w.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr(), out_f32, (int)x.size(1),
+                                        (float)eps, (int)x.size(0), cur_stream()));
+  return out;
+}
+
+// x += mult * LN(y; post) on the fp32 residual stream (in place); returns LN(x; next) in the activation type
+Tensor hy_post_layernorm_add_norm_(Tensor x, const Tensor& y, const Tensor& pw, const Tensor& pb, double mult, const Tensor& nw, const Tensor& nb,
+                                   double eps, bool act_f32) {
+  check_f32c(x, "x"); check_rows(y, "y"); check_f32c(pw, "post weight"); check_f32c(pb, "post bias"); check_f32c(nw, "next weight"); check_f32c(nb, "next bias");
+  const int64_t n = x.size(1);
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == torch::kFloat32 && x.dim() == 2 && y.size(0) == x.size(0) && y.size(1) == n && pw.numel() == n &&
+              pb.numel() == n && nw.numel() == n && nb.numel() == n);
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor xa = torch::empty({x.size(0), n}, x.options().dtype(act_type(act_f32)));
+  if (x.size(0) == 0) return xa;
+  LAUNCH_OK(b200::post_layernorm_add_norm_launch(x.data_ptr<float>(), y.data_ptr<float>(), y.stride(0), pw.data_ptr<float>(), pb.data_ptr<float>(), (float)mult,
+                                                 nw.data_ptr<float>(), nb.data_ptr<float>(), xa.data_ptr(), act_f32, (int)n, (float)eps, (int)x.size(0),
+                                                 cur_stream()));
+  return xa;
+}
+
+void hy_paged_kv_append(const Tensor& rows, int64_t k0, int64_t v0, Tensor kpool, Tensor vpool, const Tensor& slot_map) {
+  check_act(rows, "rows"); check_rows(rows, "rows"); check_i32(slot_map, "slot_mapping");
+  TORCH_CHECK(kpool.dim() == 4 && vpool.dim() == 4 && kpool.is_contiguous() && vpool.is_contiguous() && kpool.scalar_type() == rows.scalar_type() &&
+              vpool.scalar_type() == rows.scalar_type() && kpool.size(0) == vpool.size(0) && kpool.size(1) == vpool.size(1) && kpool.size(2) == vpool.size(2),
+              "pools [pages, kv_heads, page, d] in the activation type");
+  const int64_t G = kpool.size(1), dk = kpool.size(3), dv = vpool.size(3);
+  TORCH_CHECK(k0 >= 0 && v0 >= 0 && k0 + G * dk <= rows.size(1) && v0 + G * dv <= rows.size(1) && slot_map.numel() >= rows.size(0));
+  const c10::cuda::CUDAGuard guard(rows.device());
+  if (rows.size(0) == 0) return;
+  LAUNCH_OK(b200::paged_kv_append_launch(rows.data_ptr(), rows.stride(0), (int)k0, (int)v0, kpool.data_ptr(), vpool.data_ptr(), slot_map.data_ptr<int>(), (int)G,
+                                         (int)dk, (int)dv, (int)kpool.size(2), is_f32(rows), (int)rows.size(0), cur_stream()));
+}
+
+Tensor hy_diff_attention(const Tensor& q, const Tensor& kpool, const Tensor& vpool, const Tensor& block_tables, const Tensor& positions, const Tensor& cu,
+                         int64_t H, double scale, double softcap, double temp_coef, double temp_every, double lam, double eps, double out_mult,
+                         int64_t max_ctx) {
+  check_act(q, "q"); check_rows(q, "q"); check_i32(block_tables, "block_tables"); check_i32(positions, "positions"); check_i32(cu, "cu_seqlens");
+  TORCH_CHECK(kpool.dim() == 4 && vpool.dim() == 4 && kpool.is_contiguous() && vpool.is_contiguous() && kpool.scalar_type() == q.scalar_type() &&
+              vpool.scalar_type() == q.scalar_type() && kpool.size(1) == vpool.size(1) && kpool.size(2) == vpool.size(2) && kpool.size(3) % 2 == 0,
+              "pools [pages, kv_heads, page, 2 dim] / [pages, kv_heads, page, vdim] in the activation type");
+  const int64_t T = q.size(0), G = kpool.size(1), D = kpool.size(3) / 2, V = vpool.size(3);
+  TORCH_CHECK(H >= 1 && H % G == 0 && q.size(1) >= H * 2 * D && V <= 512 && temp_every > 0 && positions.numel() >= T, "differential attention: vdim <= 512");
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({T, H * V}, q.options());
+  if (T == 0) return out;
+  // few query rows over long contexts (decode): split the keys over CTAs so the grid fills the GPU; a second kernel merges the parts
+  const int nw = b200::diff_attention_warps((int)H, (int)G);
+  const int64_t ctas = T * G * ((H / G + nw - 1) / nw);
+  int64_t nsplit = 1, chunk = 1 << 30;
+  if (ctas < 2 * sm_count() && max_ctx > 256) {
+    nsplit = std::min<int64_t>({(2 * sm_count() + ctas - 1) / ctas, (max_ctx + 127) / 128, (int64_t)32});
+    chunk = ((max_ctx + nsplit - 1) / nsplit + 31) / 32 * 32;
+    nsplit = (max_ctx + chunk - 1) / chunk;
+  }
+  Tensor part;
+  if (nsplit > 1) part = torch::empty({T * H * nsplit * 2 * (V + 2)}, q.options().dtype(torch::kFloat32));
+  else chunk = 1 << 30;
+  LAUNCH_OK(b200::diff_attention_launch(q.data_ptr(), q.stride(0), kpool.data_ptr(), vpool.data_ptr(), block_tables.data_ptr<int>(), (int)block_tables.size(1),
+                                        positions.data_ptr<int>(), cu.data_ptr<int>(), (int)(cu.numel() - 1), (int)H, (int)G, (int)D, (int)V, (int)kpool.size(2),
+                                        (float)scale, (float)softcap, (float)temp_coef, (float)temp_every, (float)lam, (float)eps, (float)out_mult,
+                                        out.data_ptr(), is_f32(q), (int)T, (int)nsplit, (int)chunk, nsplit > 1 ? part.data_ptr<float>() : nullptr,
+                                        cur_stream()));
+  if (nsplit > 1) ++g_launches;
+  return out;
+}
+
+// a: fp32 [G, 2, T * (H / G), V] map outputs of a prefill run as matrix products -> (a1 - lam a2) / rms * out_mult as [T, H * V]
+Tensor hy_diff_head_norm(const Tensor& a, int64_t T, int64_t H, double lam, double eps, double out_mult, bool out_f32) {
+  check_f32c(a, "a");
+  TORCH_CHECK(a.dim() == 4 && a.size(1) == 2 && H % a.size(0) == 0 && a.size(2) == T * (H / a.size(0)) && a.size(3) <= 512);
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = torch::empty({T, H * a.size(3)}, a.options().dtype(act_type(out_f32)));
+  if (T == 0) return out;
+  LAUNCH_OK(b200::diff_head_norm_launch(a.data_ptr<float>(), (int)T, (int)H, (int)a.size(0), (int)a.size(3), (float)lam, (float)eps, (float)out_mult,
+                                        out.data_ptr(), out_f32, cur_stream()));
   return out;
 }
 
@@ -1169,14 +1264,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("cu"), py::arg("scale"), py::arg("kv_rank"), py::arg("inv_freq"), py::arg("max_ctx"), py::arg("window") = 0, py::arg("interleaved") = false);
   m.def("hy_rotate_half_", &hy_rotate_half_, py::arg("q"), py::arg("positions"), py::arg("inv_freq"), py::arg("kv_rank"), py::arg("interleaved") = false);
   m.def("hy_sink_softmax", &hy_sink_softmax, py::arg("s"), py::arg("sink"), py::arg("H"), py::arg("ctx0"), py::arg("scale"), py::arg("out_f32"),
-        py::arg("window") = 0, py::arg("k0") = 0);
+        py::arg("window") = 0, py::arg("k0") = 0, py::arg("softcap") = 0.0, py::arg("temp_coef") = 0.0, py::arg("temp_every") = 1.0);
   m.def("hy_scaled_add_norm_", &hy_scaled_add_norm_, py::arg("x"), py::arg("y"), py::arg("ls"), py::arg("w"), py::arg("eps"), py::arg("act_f32"),
         py::arg("extra") = py::none(), py::arg("gate") = py::none());
   m.def("hy_mlstm_scan", &hy_mlstm_scan);
-  m.def("hy_sigmoid_topk", &hy_sigmoid_topk);
-  m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gate"), py::arg("up"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none());
-  m.def("hy_gather_sum", &hy_gather_sum);
+  m.def("hy_sigmoid_topk", &hy_sigmoid_topk, py::arg("z"), py::arg("E"), py::arg("top"), py::arg("mode") = 0, py::arg("bias") = py::none());
+  m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gate"), py::arg("up"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none(),
+        py::arg("kind") = 0);
+  m.def("hy_gather_sum", &hy_gather_sum, py::arg("y"), py::arg("row_of"), py::arg("k"), py::arg("wts") = py::none());
   m.def("hy_expert_rows_linear", &hy_expert_rows_linear);
+  m.def("hy_layernorm_cast", &hy_layernorm_cast);
+  m.def("hy_post_layernorm_add_norm_", &hy_post_layernorm_add_norm_);
+  m.def("hy_paged_kv_append", &hy_paged_kv_append);
+  m.def("hy_diff_attention", &hy_diff_attention);
+  m.def("hy_diff_head_norm", &hy_diff_head_norm);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

@@ -7,70 +7,10 @@
 // starts from a zero state whatever its slot holds, so slots are re-used without a clear.  Activations are AT = bf16 (serving) or
 // float (exact mode); the residual stream, norms, softmax and every recurrence are fp32 in both.
 #include "hybrid.h"
-
-#include <cuda_bf16.h>
-#include <math.h>
+#include "hybrid_common.cuh"
 
 namespace b200 {
 namespace {
-
-template <typename T> __device__ __forceinline__ float ldf(const T* p);
-template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <typename T> __device__ __forceinline__ void stf(T* p, float v);
-template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
-// activations round to AT between a projection and its nonlinearity, as an unfused graph does
-template <typename T> __device__ __forceinline__ float rnd(float v);
-template <> __device__ __forceinline__ float rnd<float>(float v) { return v; }
-template <> __device__ __forceinline__ float rnd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-// 16 bytes of activations -> floats
-template <typename T> __device__ __forceinline__ void unpack16(const uint4& v, float* dst);
-template <> __device__ __forceinline__ void unpack16<float>(const uint4& v, float* dst) {
-  dst[0] = __uint_as_float(v.x); dst[1] = __uint_as_float(v.y); dst[2] = __uint_as_float(v.z); dst[3] = __uint_as_float(v.w);
-}
-template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float* dst) {
-  const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { dst[2 * i] = __uint_as_float(w[i] << 16); dst[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
-}
-
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
-__device__ __forceinline__ float softplus_f(float v) { return v > 30.f ? v : log1pf(expf(v)); }
-__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
-__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.f + erff(z * 0.7071067811865476f)); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// sum over the block (blockDim.x <= 1024, multiple of 32); every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (l == 0) red[w] = v;
-  __syncthreads();
-  float t = l < nw ? red[l] : 0.f;
-  return warp_sum(t);
-}
-// sequence of row t: largest b with cu[b] <= t
-__device__ __forceinline__ int seq_of(const int* cu, int B, int t) {
-  int lo = 0, hi = B - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (cu[mid] <= t) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
 
 // ---------------------------------------------------------------------------------------------------------- gathers
 template <typename TT, typename OT>
@@ -498,27 +438,33 @@ __global__ void rotate_half_kernel(AT* __restrict__ q, const int* __restrict__ p
 
 // row r = (token t, head h) of raw scores [rows, n]; column j is the key at position k0 + j; the query sits at position ctx0 + t and sees
 // keys at positions <= its own (and > its own - window when window > 0); p_j = e^(s_j scale - m) / (e^(sink_h - m) + sum), the sink
-// term only when sink != nullptr
+// term only when sink != nullptr.  temp_coef != 0: the query's scores are multiplied by 1 + temp_coef ln(floor((qp + 1) / temp_every) + 1);
+// softcap > 0: s <- softcap tanh(s / softcap) after the scaling
+struct ScoreMap {
+  float scale, softcap;
+  __device__ __forceinline__ float operator()(float v) const { v *= scale; return softcap > 0.f ? softcap * tanhf(v / softcap) : v; }
+};
 template <typename AT>
-__global__ void sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, int H, int n, int ctx0, float scale,
-                                    AT* __restrict__ out, int window, int k0) {
+__global__ void sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, int H, int n, int ctx0, float scale0,
+                                    AT* __restrict__ out, int window, int k0, float softcap, float temp_coef, float temp_every) {
   __shared__ float red[32];
   const long long r = blockIdx.x;
   const int t = (int)(r / H), h = (int)(r % H), qp = ctx0 + t;
+  const ScoreMap f{temp_coef != 0.f ? scale0 * (1.f + temp_coef * logf(floorf((float)(qp + 1) / temp_every) + 1.f)) : scale0, softcap};
   const int nv = max(0, min(n, qp - k0 + 1)), j_lo = window > 0 ? max(0, qp - window + 1 - k0) : 0;
   const float* row = s + r * n;
   const float sk = sink != nullptr ? sink[h] : -INFINITY;
   float m = sk;
-  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) m = fmaxf(m, row[j] * scale);
+  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) m = fmaxf(m, f(row[j]));
   m = warp_max(m);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (l == 0) red[w] = m;
   __syncthreads();
   m = warp_max(l < nw ? red[l] : -INFINITY);
   float sum = 0.f;
-  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) sum += expf(row[j] * scale - m);
+  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) sum += expf(f(row[j]) - m);
   const float inv = 1.f / (block_sum(sum, red) + (sink != nullptr ? expf(sk - m) : 0.f));
-  for (int j = threadIdx.x; j < n; j += blockDim.x) stf<AT>(out + r * n + j, (j >= j_lo && j < nv) ? expf(row[j] * scale - m) * inv : 0.f);
+  for (int j = threadIdx.x; j < n; j += blockDim.x) stf<AT>(out + r * n + j, (j >= j_lo && j < nv) ? expf(f(row[j]) - m) * inv : 0.f);
 }
 
 // ---------------------------------------------------------------------------------------------------------- pre-norm residual step
@@ -664,12 +610,14 @@ __global__ void mlstm_scan_kernel(MlstmArgs a, int PB, int R, int kTok) {
 }
 
 // ---------------------------------------------------------------------------------------------------------- mixture of experts
-// Router on fp32 logits: scores sigmoid(z), the `top` largest (ties: lowest id), weights = the chosen scores.  One warp per token.
-__global__ void sigmoid_topk_kernel(const float* __restrict__ z, long long ld_z, int E, int top, int* __restrict__ idx, float* __restrict__ w) {
+// Router on fp32 logits, the `top` largest scores (ties: lowest id).  One warp per token.  mode 0: scores sigmoid(z), weights = the chosen
+// scores; mode 1: scores z + bias (bias nullable), weights = softmax over the chosen scores alone.
+__global__ void sigmoid_topk_kernel(const float* __restrict__ z, long long ld_z, const float* __restrict__ bias, int mode, int E, int top,
+                                    int* __restrict__ idx, float* __restrict__ w) {
   extern __shared__ float sc[];             // [E]
   const long long t = blockIdx.x;
   const int lane = threadIdx.x;
-  for (int e = lane; e < E; e += 32) sc[e] = sigmoid_f(z[t * ld_z + e]);
+  for (int e = lane; e < E; e += 32) sc[e] = mode == 0 ? sigmoid_f(z[t * ld_z + e]) : z[t * ld_z + e] + (bias != nullptr ? bias[e] : 0.f);
   __syncwarp();
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY; int bi = 0x7fffffff;
@@ -683,18 +631,26 @@ __global__ void sigmoid_topk_kernel(const float* __restrict__ z, long long ld_z,
     if (lane == 0) { idx[t * top + j] = bi; w[t * top + j] = best; sc[bi] = -INFINITY; }
     __syncwarp();
   }
+  if (mode == 1 && lane == 0) {             // the first chosen score is the largest
+    const float m = w[t * top];
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) sum += expf(w[t * top + j] - m);
+    for (int j = 0; j < top; ++j) w[t * top + j] = expf(w[t * top + j] - m) / sum;
+  }
 }
 
 // gate rows g and up rows u (F wide each, own row strides) -> g' sigmoid(1.702 g') (u' + 1),  g' = min(s g, limit), u' = clamp(s u, +-limit).  Block i handles row
 // row_of[i] with scale s = scale[i] (both nullable: row i, scale 1): scaling a projection's output equals scaling its input.
+// kind 1: silu(g) u s instead (no clamp; the scale multiplies the product, i.e. the input of the down projection).
 template <typename AT>
 __global__ void clamped_glu_kernel(const AT* __restrict__ gp, long long ld_g, const AT* __restrict__ up, long long ld_u, int F, float limit,
-                                   const int* __restrict__ row_of, const float* __restrict__ scale, AT* __restrict__ out) {
+                                   const int* __restrict__ row_of, const float* __restrict__ scale, AT* __restrict__ out, int kind) {
   const long long r = row_of != nullptr ? row_of[blockIdx.x] : blockIdx.x;
   const float s = scale != nullptr ? scale[blockIdx.x] : 1.f;
   const AT* grow = gp + r * ld_g;
   const AT* urow = up + r * ld_u;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < F; c += gridDim.y * blockDim.x) {
+    if (kind == 1) { stf<AT>(out + r * F + c, silu_f(ldf<AT>(grow + c)) * ldf<AT>(urow + c) * s); continue; }
     const float g = fminf(s * ldf<AT>(grow + c), limit), u = fminf(fmaxf(s * ldf<AT>(urow + c), -limit), limit);
     stf<AT>(out + r * F + c, g * sigmoid_f(1.702f * g) * (u + 1.f));
   }
@@ -717,22 +673,20 @@ __global__ void expert_rows_linear_kernel(const AT* __restrict__ x, long long ld
   if (lane == 0) stf<OT>(out + i * N + n, acc);
 }
 
-// out[t] = sum_j y[row_of[t * k + j]]   (fp32): the routed experts' results back in token order
-__global__ void gather_sum_kernel(const float* __restrict__ y, const int* __restrict__ row_of, int k, int n, float* __restrict__ out) {
+// out[t] = sum_j wts[t * k + j] y[row_of[t * k + j]]   (fp32; wts nullable: 1; row_of nullable: row t * k + j): the routed experts' results
+// back in token order
+__global__ void gather_sum_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ wts, int k, int n,
+                                  float* __restrict__ out) {
   const long long t = blockIdx.x;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
     float acc = 0.f;
-    for (int j = 0; j < k; ++j) acc += y[(long long)row_of[t * k + j] * n + c];
+    for (int j = 0; j < k; ++j) {
+      const long long r = row_of != nullptr ? row_of[t * k + j] : t * k + j;
+      acc += (wts != nullptr ? wts[t * k + j] : 1.f) * y[r * n + c];
+    }
     out[t * n + c] = acc;
   }
 }
-
-inline cudaError_t last() { return cudaGetLastError(); }
-#define AT_DISPATCH(f32, ...)                                      \
-  do {                                                             \
-    if (f32) { using AT = float; __VA_ARGS__; }                    \
-    else { using AT = __nv_bfloat16; __VA_ARGS__; }                \
-  } while (0)
 
 }  // namespace
 
@@ -839,8 +793,9 @@ cudaError_t rotate_half_launch(void* q, const int* positions, const float* inv_f
 }
 
 cudaError_t sink_softmax_launch(const float* sc, const float* sink, int H, int n, int ctx0, float scale, void* out, bool f32, long long rows,
-                                int window, int k0, cudaStream_t s) {
-  AT_DISPATCH(f32, (sink_softmax_kernel<AT><<<(unsigned)rows, 256, 0, s>>>(sc, sink, H, n, ctx0, scale, (AT*)out, window, k0)));
+                                int window, int k0, float softcap, float temp_coef, float temp_every, cudaStream_t s) {
+  AT_DISPATCH(f32, (sink_softmax_kernel<AT><<<(unsigned)rows, 256, 0, s>>>(sc, sink, H, n, ctx0, scale, (AT*)out, window, k0, softcap, temp_coef,
+                                                                          temp_every)));
   return last();
 }
 
@@ -901,16 +856,17 @@ cudaError_t mlstm_scan_launch(const void* in, long long ld_in, const float* gate
   return last();
 }
 
-cudaError_t sigmoid_topk_launch(const float* z, long long ld_z, int E, int top, int* idx, float* w, int T, cudaStream_t s) {
+cudaError_t router_topk_launch(const float* z, long long ld_z, const float* bias, int mode, int E, int top, int* idx, float* w, int T,
+                               cudaStream_t s) {
   if (top > E || (size_t)E * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
-  sigmoid_topk_kernel<<<T, 32, E * sizeof(float), s>>>(z, ld_z, E, top, idx, w);
+  sigmoid_topk_kernel<<<T, 32, E * sizeof(float), s>>>(z, ld_z, bias, mode, E, top, idx, w);
   return last();
 }
 
 cudaError_t clamped_glu_launch(const void* g, long long ld_g, const void* u, long long ld_u, int F, float limit, const int* row_of,
-                               const float* scale, void* out, bool f32, int rows, cudaStream_t s) {
+                               const float* scale, void* out, bool f32, int rows, int kind, cudaStream_t s) {
   dim3 grid(rows, (F + 1023) / 1024);
-  AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)g, ld_g, (const AT*)u, ld_u, F, limit, row_of, scale, (AT*)out)));
+  AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)g, ld_g, (const AT*)u, ld_u, F, limit, row_of, scale, (AT*)out, kind)));
   return last();
 }
 
@@ -923,9 +879,9 @@ cudaError_t expert_rows_linear_launch(const void* x, long long ld_x, int div, co
   return last();
 }
 
-cudaError_t gather_sum_launch(const float* y, const int* row_of, int k, int n, float* out, int T, cudaStream_t s) {
+cudaError_t gather_sum_launch(const float* y, const int* row_of, const float* wts, int k, int n, float* out, int T, cudaStream_t s) {
   dim3 grid(T, (n + 1023) / 1024);
-  gather_sum_kernel<<<grid, 256, 0, s>>>(y, row_of, k, n, out);
+  gather_sum_kernel<<<grid, 256, 0, s>>>(y, row_of, wts, k, n, out);
   return last();
 }
 
