@@ -56,11 +56,14 @@ def diff_attention_mixer(h, p, m, eps):
     return out.reshape(T, H * V) @ p["o"].T
 
 
-def moe_ff(h, p, mlp):
+def moe_ff(h, p, mlp, gaps=None):
     """``p``: ``router``, ``router.b``, ``e<i>.gate|up|down``.  The ``top`` largest logits choose the experts, a softmax over those logits
-    alone weighs their outputs."""
+    alone weighs their outputs.  ``gaps``: list that receives the distance between the last chosen and the first rejected logit."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ p["router"].T + p["router.b"]
+    if gaps is not None and top < E:
+        srt = torch.sort(z, -1, descending=True).values
+        gaps.append(float((srt[:, top - 1] - srt[:, top]).min()))
     val, idx = torch.topk(z, top, dim=-1)
     wt = torch.softmax(val, -1)
     out = torch.zeros(h.shape[0], p["e0.down"].shape[0], dtype=h.dtype)
@@ -77,7 +80,7 @@ def sub(sd, prefix):
     return {k[len(prefix):]: v for k, v in sd.items() if k.startswith(prefix)}
 
 
-def forward(cfg, sd, tokens, dtype=torch.float64, layers_out=None):
+def forward(cfg, sd, tokens, dtype=torch.float64, layers_out=None, gaps=None):
     """Logits ``[T, vocab]`` of one sequence; ``layers_out``: list that receives the residual stream after every layer."""
     sd = {k: v.to(dtype) for k, v in sd.items()}
     eps, mult = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
@@ -89,11 +92,18 @@ def forward(cfg, sd, tokens, dtype=torch.float64, layers_out=None):
         x = x + mult * layer_norm(y, sd[p + "norm1b"], sd[p + "norm1b.b"], eps)
         if L.get("mlp"):
             assert L["mlp"]["kind"] == "moe"
-            y = moe_ff(layer_norm(x, sd[p + "norm2"], sd[p + "norm2.b"], eps), sub(sd, p + "mlp."), L["mlp"])
+            y = moe_ff(layer_norm(x, sd[p + "norm2"], sd[p + "norm2.b"], eps), sub(sd, p + "mlp."), L["mlp"], gaps)
             x = x + mult * layer_norm(y, sd[p + "norm2b"], sd[p + "norm2b.b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     return layer_norm(x, sd["final.norm"], sd["final.norm.b"], eps) @ sd["embed"].T
+
+
+def min_router_gap(cfg, sd, tokens):
+    """Smallest distance between a chosen and a rejected router logit over all tokens and layers (inf without such a choice)."""
+    gaps = []
+    forward(cfg, sd, tokens, gaps=gaps)
+    return min(gaps) if gaps else float("inf")
 
 
 def tensor_shapes(cfg):
