@@ -85,6 +85,9 @@ def pick(cfgd, sd, dtype, make, seed, gap=0.08, tries=200):
     raise AssertionError("no sequence without a close routing call found")
 
 
+SHOWS = 1e-2      # a fault must move the logits by this share of their largest: 50 times the exact-mode tolerance (bf16 runs are less sharp)
+
+
 def close(a, b, tol):
     a, b = a.float().cpu(), b.float().cpu()
     err = (a - b).abs().max().item() / max(1.0, b.abs().max().item())
@@ -220,7 +223,7 @@ def test_temperature_steps_show(device, dtype, tol):
     for every, p in ((6, 5), (8, 6)):                 # one earlier: position 5 already stepped; one later: position 6 not yet
         other = copy.deepcopy(cfgd)
         other["layers"][0]["mixer"]["q_temp"]["every"] = every
-        assert (oracle.forward(other, sd, t)[p] - want[p]).abs().max() > 4 * tol * want.abs().max()
+        assert (oracle.forward(other, sd, t)[p] - want[p]).abs().max() > SHOWS * want.abs().max()
     close(run_whole(model, t), want, tol)
     close(decode_after(model, t, 4), want, tol)
 
@@ -239,7 +242,7 @@ def test_far_key_and_capped_scores(device, dtype, tol):
         want = oracle.forward(cfgd, sd, t)
         lost = list(t)
         lost[1] = (t[1] + 1) % 96                     # another token far back: the logits where it is sought move
-        need = 4 * tol * want.abs().max()
+        need = 5 * SHOWS * want.abs().max()
         if (oracle.forward(cfgd, sd, lost)[50:] - want[50:]).abs().max() > need and (oracle.forward(nocap, sd, t)[50:] - want[50:]).abs().max() > need:
             break
     else:
@@ -261,7 +264,7 @@ def test_lambda_and_head_norm_show(device, dtype, tol):
     t = pick(cfgd, sd, dtype, lambda s: toks(20, seed=s), 3)
     want = oracle.forward(cfgd, sd, t)
     plain = {k: (torch.zeros_like(v) if ".mix.l" in k else v) for k, v in sd.items()}
-    assert (oracle.forward(cfgd, plain, t) - want).abs().max() > 4 * tol * want.abs().max()
+    assert (oracle.forward(cfgd, plain, t) - want).abs().max() > 5 * SHOWS * want.abs().max()
     close(run_whole(model, t), want, tol)
     close(decode_after(model, t, 9), want, tol)
 
