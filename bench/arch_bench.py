@@ -1,11 +1,14 @@
-"""Hybrid designs beside the framework's closest existing model.  ``--arch gusolorn``: Gusolorn beside Perelorn (the other hybrid stack:
+"""Hybrid designs beside the framework's closest existing model.  ``--arch gifetar``: Gifetar beside Gusolorn (the other stack with an fp32
+residual stream, multi-head attention over paged rows and routed experts) at equal width, depth, heads and experts, and each of its
+kernels beside the like kernel (differential attention / latent attention, layer-norm residual step / scaled residual add + norm,
+SiLU-GLU experts / clamped-GLU experts, softmax / sigmoid top-k router).  ``--arch gusolorn``: Gusolorn beside Perelorn (the other hybrid stack:
 latent attention + recurrent layers) at equal width and depth, and each of its kernels beside the like kernel (mLSTM scan / decayed
 linear-attention scan, windowed sink-free latent attention / latent attention with a sink, scaled residual add + norm / output-side norm +
 add, clamped-GLU experts / the SwiGLU expert path).  ``--arch perelorn``: Perelorn beside the framework's closest existing model (DeepSeek-V2 with dense feed-forwards: latent attention, same width and
 about the same weight bytes), random weights, bf16, one GPU: prefill and decode throughput of the whole stack, and the time of each
 new kernel against the HBM roofline (``MEASURED_PEAKS.json``), with the like kernel of the closest model where there is one.
 
-    python bench.py --arch perelorn|gusolorn [--arch-sizes 1024,2048]        (prints one JSON line per measurement)
+    python bench.py --arch perelorn|gusolorn|gifetar [--arch-sizes 1024,2048]        (prints one JSON line per measurement)
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, an L2 flush (256 MiB write) before every timed run, median of 7.
 """
@@ -20,7 +23,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from mlx_sharding_b200.config import deepseek_v2_lite_config, gusolorn_config, perelorn_config  # noqa: E402
+from mlx_sharding_b200.config import deepseek_v2_lite_config, gifetar_config, gusolorn_config, perelorn_config  # noqa: E402
 from mlx_sharding_b200.ops.meta import BatchMeta  # noqa: E402
 from mlx_sharding_b200.parallel.pipeline import StageExecutor  # noqa: E402
 from mlx_sharding_b200.utils.loader import random_model  # noqa: E402
@@ -233,9 +236,101 @@ def gusolorn_main(sizes=(1024, 2048)):
         print(json.dumps(dict(bench="arch-kernel", roofline=f"{hbm} GB/s {tag}", **row)), flush=True)
 
 
+def gifetar_kernel_table(width, dev, hbm):
+    """Gifetar's kernels alone at one layer's shapes beside the like kernel of Gusolorn; bytes = what the kernel must move.  The prefill
+    attention is bound by arithmetic, so it also reports TFLOP/s (both maps: 2 * heads * (dim + vdim) multiply-adds per visible key)."""
+    from mlx_sharding_b200.ops import b200 as O
+    from mlx_sharding_b200.ops.weights import LinearWeight
+
+    rows = []
+    H, G, D, V, W = 16, 4, 64, 128, width
+    Hl, Lr, R = 16, 512, 64
+    bf = torch.bfloat16
+
+    def add(name, ms, nbytes, like=None, flops=None):
+        r = dict(kernel=name, ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_hbm=round(nbytes / ms / 1e6 / hbm, 3))
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+        if like:
+            r["like_kernel"] = like
+        rows.append(r)
+
+    for phase, B, q, ctx0 in (("decode", 64, 1, 2047), ("prefill", 1, 2048, 0)):
+        meta, _ = step_meta(B, q, ctx0, dev, False)
+        T, npg = B * q, 1 + B * ((ctx0 + q + PS - 1) // PS)
+        kp, vp = torch.randn(npg, G, PS, 2 * D, device=dev).to(bf), torch.randn(npg, G, PS, V, device=dev).to(bf)
+        u = torch.randn(T, (H + G) * 2 * D + G * V, device=dev).to(bf)
+        nbytes = B * (ctx0 + q) * G * (2 * D + V) * 2 + T * H * (2 * D + V) * 2
+        pairs = B * (ctx0 + q) if q == 1 else (ctx0 + q) * (ctx0 + q + 1) // 2
+        flops = 2 * 2 * H * (D + V) * pairs
+        args = (H, D ** -0.5, 50.0, 0.1, 1024.0, 0.7, 1e-5, 0.2, bf)
+        ms = timed(lambda: O.diff_attention(u, kp, vp, meta, *args))
+        add(f"diff_attention {phase}", ms, nbytes, flops=flops)
+        ms = timed(lambda: O.paged_kv_append(u, H * 2 * D, (H + G) * 2 * D, kp, vp, meta))
+        add(f"paged_kv_append {phase}", ms, 2 * T * G * (2 * D + V) * 2)
+        pool = torch.randn(npg, 1, PS, Lr + R, device=dev).to(bf)
+        qq = torch.randn(T, Hl, Lr + R, device=dev).to(bf)
+        inv = torch.rand(R // 2, device=dev)
+        lbytes = B * (ctx0 + q) * (Lr + R) * 2 + T * Hl * (2 * Lr + R) * 2
+        lflops = 2 * Hl * (2 * Lr + R) * pairs
+        ms = timed(lambda: O.latent_attention(qq, pool, None, meta, 0.07, Lr, inv, window=0, interleaved=True))
+        add(f"latent_attention(no sink, no window) (Gusolorn) {phase}", ms, lbytes, like=f"diff_attention {phase}", flops=lflops)
+        if phase == "prefill":
+            ms = timed(lambda: O.diff_attention_prefill(u, kp, vp, meta, *args))
+            add("diff_attention_prefill(GEMM form) prefill", ms, nbytes, flops=flops)
+            ms = timed(lambda: O.latent_attention_prefill(qq.clone(), pool, None, meta, 0.07, Lr, inv, window=0, interleaved=True))
+            add("latent_attention_prefill(GEMM form) (Gusolorn) prefill", ms, lbytes, like="diff_attention_prefill(GEMM form) prefill", flops=lflops)
+        x, y = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+        v4 = [torch.randn(W, device=dev) for _ in range(4)]
+        ms = timed(lambda: O.post_layernorm_add_norm_(x, y, v4[0], v4[1], 0.5, v4[2], v4[3], 1e-5, bf))
+        add(f"post_layernorm_add_norm {phase}", ms, T * W * (4 + 4 + 4 + 2))
+        ms = timed(lambda: O.scaled_add_norm_(x, y, v4[0], v4[1], 1e-5, bf))
+        add(f"scaled_add_norm (Gusolorn) {phase}", ms, T * W * (4 + 4 + 4 + 2), like=f"post_layernorm_add_norm {phase}")
+        ms = timed(lambda: O.layernorm_cast(x, v4[0], v4[1], 1e-5, bf))
+        add(f"layernorm_cast {phase}", ms, T * W * (4 + 2))
+        ms = timed(lambda: O.rmsnorm_cast(x, v4[0], 1e-5, bf))
+        add(f"rmsnorm_cast (Gusolorn) {phase}", ms, T * W * (4 + 2), like=f"layernorm_cast {phase}")
+        # routed experts: 16 experts, top 2, expert width 1024
+        E, F, k = 16, 1024, 2
+        xa = torch.randn(T, W, device=dev).to(bf)
+        wg, wu = (LinearWeight(weight=(torch.randn(E, F, W, device=dev) * W ** -0.5).to(bf)) for _ in range(2))
+        wd = LinearWeight(weight=(torch.randn(E, W, F, device=dev) * F ** -0.5).to(bf))
+        z, zb = torch.randn(T, E, device=dev), torch.randn(E, device=dev)
+        idx, wts = O.softmax_topk(z, zb, E, k)
+        touched = min(E, T * k)
+        nbytes = touched * 3 * F * W * 2 + T * W * (2 + 4) + T * k * (2 * W * 2 + 2 * F * 2 + 2 * W * 4)
+        ms = timed(lambda: O.moe_glu_experts(xa, idx, wts, wg, wu, wd))
+        add(f"moe_glu_experts {phase}", ms, nbytes)
+        ms = timed(lambda: O.moe_clamped_experts(xa, idx, wts, wg, wu, wd, 7.0))
+        add(f"moe_clamped_experts (Gusolorn) {phase}", ms, nbytes, like=f"moe_glu_experts {phase}")
+        ms = timed(lambda: O.softmax_topk(z, zb, E, k))
+        add(f"softmax_topk {phase}", ms, T * E * 4 + T * k * 8)
+        ms = timed(lambda: O.sigmoid_topk(z, E, k))
+        add(f"sigmoid_topk (Gusolorn) {phase}", ms, T * E * 4 + T * k * 8, like=f"softmax_topk {phase}")
+    return rows
+
+
+def gifetar_main(sizes=(1024, 2048)):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tag = peaks()
+    for width in sizes:
+        for name, cfg in (("gifetar", gifetar_config(width=width, vocab=32000, layers=8, heads=16, kv_heads=4, dim=64, vdim=128, experts=16, top=2, expert_ff=width // 2)),
+                          ("gusolorn", gusolorn_config(width=width, vocab=32000, blocks=2, heads=16, ff=4 * width, experts=16, top=2, expert_ff=width // 2))):
+            m = random_model(cfg, dtype=torch.bfloat16, device=dev, seed=1)
+            r = model_runs(name, m, 32, 1024, 2048, dev, name != "gifetar")
+            print(json.dumps(dict(bench="arch", model=name, width=width, layers=len(cfg["layers"]), **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})), flush=True)
+            del m
+            torch.cuda.empty_cache()
+    for row in gifetar_kernel_table(sizes[-1], dev, hbm):
+        print(json.dumps(dict(bench="arch-kernel", roofline=f"{hbm} GB/s {tag}", **row)), flush=True)
+
+
 def main(sizes=(1024, 2048), arch="perelorn"):
     if arch == "gusolorn":
         return gusolorn_main(sizes)
+    if arch == "gifetar":
+        return gifetar_main(sizes)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     hbm, tag = peaks()
