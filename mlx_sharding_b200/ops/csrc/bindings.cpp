@@ -1148,8 +1148,9 @@ Tensor hy_diff_attention(const Tensor& q, const Tensor& kpool, const Tensor& vpo
   const int nw = b200::diff_attention_warps((int)H, (int)G);
   const int64_t ctas = T * G * ((H / G + nw - 1) / nw);
   int64_t nsplit = 1, chunk = 1 << 30;
-  if (ctas < 2 * sm_count() && max_ctx > 256) {
-    nsplit = std::min<int64_t>({(2 * sm_count() + ctas - 1) / ctas, (max_ctx + 127) / 128, (int64_t)32});
+  // (a CTA waits for each tile of keys before it computes on it: several resident CTAs per SM hide that wait)
+  if (ctas < 6 * sm_count() && max_ctx > 256) {
+    nsplit = std::min<int64_t>({(6 * sm_count() + ctas - 1) / ctas, (max_ctx + 127) / 128, (int64_t)32});
     chunk = ((max_ctx + nsplit - 1) / nsplit + 31) / 32 * 32;
     nsplit = (max_ctx + chunk - 1) / chunk;
   }

@@ -77,32 +77,39 @@ struct DiffAttnArgs {
 
 constexpr int kDiffTile = 32;               // keys per tile: one per lane
 
-// o = a1 - lam a2,  o / sqrt(mean(o^2) + eps) * out_mult;  register i of a lane holds value column lane + 32 i
-template <typename AT, int NPL>
+// value column of register i of a lane: VEC (vdim a multiple of 128) 4 lane + 128 (i / 4) + i % 4 — four adjacent columns per 16-byte
+// shared-memory load —, else lane + 32 i
+template <bool VEC>
+__device__ __forceinline__ int vcol(int lane, int i) { return VEC ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i; }
+
+// o = a1 - lam a2,  o / sqrt(mean(o^2) + eps) * out_mult
+template <typename AT, int NPL, bool VEC>
 __device__ __forceinline__ void diff_finish(const float* a1, const float* a2, int V, float lam, float eps, float out_mult, AT* orow, int lane) {
   float o[NPL], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
-    const int d = lane + 32 * i;
+    const int d = vcol<VEC>(lane, i);
     o[i] = d < V ? a1[i] - lam * a2[i] : 0.f;
     ss += o[i] * o[i];
   }
   const float r = out_mult / sqrtf(warp_sum(ss) / (float)V + eps);
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
-    const int d = lane + 32 * i;
+    const int d = vcol<VEC>(lane, i);
     if (d < V) stf<AT>(orow + d, o[i] * r);
   }
 }
 
 // grid (tokens, G * ceil((H/G) / warps), key splits); one warp per query head, the warps of a CTA share one key / value head whose
 // tile of kDiffTile keys and values is staged in shared memory as floats.  Lane j scores key j of the tile for both maps; the two
-// running softmaxes (m, l) and accumulators live in registers, lane l owning value columns l + 32 i.
-template <typename AT, int NPL>
+// running softmaxes (m, l) and accumulators live in registers, each lane owning the value columns vcol(lane, i).
+// VEC (2 dim a multiple of 8, vdim a multiple of 128): 16-byte shared-memory loads in both phases, key rows padded by 4 floats; else
+// scalar loads, key rows padded by 1.
+template <typename AT, int NPL, bool VEC>
 __global__ void diff_attention_kernel(DiffAttnArgs a) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int D2 = 2 * a.D, V = a.V, ldk = D2 + 1;
+  const int D2 = 2 * a.D, V = a.V, ldk = VEC ? D2 + 4 : D2 + 1;
   float* qs = smem;                         // [nw][2D]
   float* ks = qs + nw * D2;                 // [tile][2D + 1]
   float* vs = ks + kDiffTile * ldk;         // [tile][V]
@@ -134,7 +141,17 @@ __global__ void diff_attention_kernel(DiffAttnArgs a) {
       const AT* vsrc = (const AT*)a.vpool + base * V;
       float* kd = ks + jj * ldk;
       float* vd = vs + jj * V;
-      if (vec) {
+      if (VEC) {                                        // 16-byte stores too: rows and chunks are 16-byte aligned
+        for (int c = lane; c < (D2 + V) / E; c += 32) {
+          const bool isk = c < D2 / E;
+          const int cc = isk ? c : c - D2 / E;
+          float f[E];
+          unpack16<AT>(*reinterpret_cast<const uint4*>((isk ? ksrc : vsrc) + cc * E), f);
+          float* dst = (isk ? kd : vd) + cc * E;
+#pragma unroll
+          for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+        }
+      } else if (vec) {
         for (int c = lane; c < D2 / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(ksrc + c * E), kd + c * E);
         for (int c = lane; c < V / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(vsrc + c * E), vd + c * E);
       } else {
@@ -148,7 +165,18 @@ __global__ void diff_attention_kernel(DiffAttnArgs a) {
     if (lane < nk) {
       const float* kr = ks + lane * ldk;
       float d1 = 0.f, d2 = 0.f;
-      for (int d = 0; d < a.D; ++d) { d1 += qh[d] * kr[d]; d2 += qh[a.D + d] * kr[a.D + d]; }
+      if (VEC) {
+        const float4* q4 = reinterpret_cast<const float4*>(qh);
+        const float4* k4 = reinterpret_cast<const float4*>(kr);
+        const int n4 = a.D >> 2;
+        for (int d = 0; d < n4; ++d) {
+          const float4 x = q4[d], y = k4[d], z = q4[n4 + d], w = k4[n4 + d];
+          d1 += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+          d2 += z.x * w.x + z.y * w.y + z.z * w.z + z.w * w.w;
+        }
+      } else {
+        for (int d = 0; d < a.D; ++d) { d1 += qh[d] * kr[d]; d2 += qh[a.D + d] * kr[a.D + d]; }
+      }
       s1 = d1 * mul; s2 = d2 * mul;
       if (a.softcap > 0.f) { s1 = a.softcap * tanhf(s1 / a.softcap); s2 = a.softcap * tanhf(s2 / a.softcap); }
     }
@@ -162,10 +190,20 @@ __global__ void diff_attention_kernel(DiffAttnArgs a) {
     for (int jj = 0; jj < nk; ++jj) {
       const float w1 = __shfl_sync(0xffffffffu, p1, jj), w2 = __shfl_sync(0xffffffffu, p2, jj);
       const float* vr = vs + jj * V;
+      if (VEC) {
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < V) { const float v = vr[d]; o1[i] += w1 * v; o2[i] += w2 * v; }
+        for (int i = 0; i < NPL / 4; ++i)
+          if (128 * i < V) {
+            const float4 c = *reinterpret_cast<const float4*>(vr + 4 * lane + 128 * i);
+            o1[4 * i] += w1 * c.x; o1[4 * i + 1] += w1 * c.y; o1[4 * i + 2] += w1 * c.z; o1[4 * i + 3] += w1 * c.w;
+            o2[4 * i] += w2 * c.x; o2[4 * i + 1] += w2 * c.y; o2[4 * i + 2] += w2 * c.z; o2[4 * i + 3] += w2 * c.w;
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          const int d = lane + 32 * i;
+          if (d < V) { const float v = vr[d]; o1[i] += w1 * v; o2[i] += w2 * v; }
+        }
       }
     }
   }
@@ -174,13 +212,13 @@ __global__ void diff_attention_kernel(DiffAttnArgs a) {
     const float i1 = 1.f / l1, i2 = 1.f / l2;          // the query's own position is always visible: l > 0
 #pragma unroll
     for (int i = 0; i < NPL; ++i) { o1[i] *= i1; o2[i] *= i2; }
-    diff_finish<AT, NPL>(o1, o2, V, a.lam, a.eps, a.out_mult, (AT*)a.out + ((long long)t * a.H + h) * V, lane);
+    diff_finish<AT, NPL, VEC>(o1, o2, V, a.lam, a.eps, a.out_mult, (AT*)a.out + ((long long)t * a.H + h) * V, lane);
   } else {
     float* pp = a.part + (((long long)t * a.H + h) * a.nsplit + blockIdx.z) * 2 * (V + 2);
     if (lane == 0) { pp[0] = m1; pp[1] = l1; pp[V + 2] = m2; pp[V + 3] = l2; }
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
-      const int d = lane + 32 * i;
+      const int d = vcol<VEC>(lane, i);
       if (d < V) { pp[2 + d] = o1[i]; pp[V + 4 + d] = o2[i]; }
     }
   }
@@ -211,7 +249,7 @@ __global__ void diff_combine_kernel(const float* __restrict__ part, int V, int n
 #pragma unroll
     for (int i = 0; i < NPL; ++i) acc[c][i] *= inv;
   }
-  diff_finish<AT, NPL>(acc[0], acc[1], V, lam, eps, out_mult, out + th * V, lane);
+  diff_finish<AT, NPL, false>(acc[0], acc[1], V, lam, eps, out_mult, out + th * V, lane);
 }
 
 // prefill as matrix products: a1, a2 fp32 [G, 2, T * Rg, V] (row t * Rg + r of block (g, c) = token t, head g * Rg + r, map c) ->
@@ -226,7 +264,7 @@ __global__ void diff_head_norm_kernel(const float* __restrict__ a, int T, int H,
   float a1[NPL], a2[NPL];
 #pragma unroll
   for (int i = 0; i < NPL; ++i) { const int d = lane + 32 * i; a1[i] = d < V ? p1[d] : 0.f; a2[i] = d < V ? p2[d] : 0.f; }
-  diff_finish<AT, NPL>(a1, a2, V, lam, eps, out_mult, out + th * V, lane);
+  diff_finish<AT, NPL, false>(a1, a2, V, lam, eps, out_mult, out + th * V, lane);
 }
 
 }  // namespace
@@ -255,18 +293,24 @@ int diff_attention_warps(int H, int G) {
   return Rg < 1 ? 1 : (Rg > 8 ? 8 : Rg);
 }
 
-template <typename AT, int NPL>
-static cudaError_t diff_attention_launch_t(const DiffAttnArgs& a, int T, cudaStream_t s) {
+template <typename AT, int NPL, bool VEC>
+static cudaError_t diff_attention_launch_v(const DiffAttnArgs& a, int T, cudaStream_t s) {
   const int nw = diff_attention_warps(a.H, a.G), Rg = a.H / a.G, nb = (Rg + nw - 1) / nw;
-  const size_t smem = ((size_t)nw * 2 * a.D + (size_t)kDiffTile * (2 * a.D + 1) + (size_t)kDiffTile * a.V) * sizeof(float);
+  const size_t smem = ((size_t)nw * 2 * a.D + (size_t)kDiffTile * (2 * a.D + (VEC ? 4 : 1)) + (size_t)kDiffTile * a.V) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  auto k = diff_attention_kernel<AT, NPL>;
+  auto k = diff_attention_kernel<AT, NPL, VEC>;
   if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
   k<<<dim3(T, a.G * nb, a.nsplit), nw * 32, smem, s>>>(a);
   cudaError_t e = last();
   if (e != cudaSuccess || a.nsplit == 1) return e;
   diff_combine_kernel<AT, NPL><<<T * a.H, 32, 0, s>>>(a.part, a.V, a.nsplit, a.lam, a.eps, a.out_mult, (AT*)a.out);
   return last();
+}
+
+template <typename AT, int NPL>
+static cudaError_t diff_attention_launch_t(const DiffAttnArgs& a, int T, cudaStream_t s) {
+  if (NPL % 4 == 0 && (2 * a.D) % 8 == 0 && a.V % 128 == 0) return diff_attention_launch_v<AT, NPL, true>(a, T, s);
+  return diff_attention_launch_v<AT, NPL, false>(a, T, s);
 }
 
 cudaError_t diff_attention_launch(const void* q, long long ld_q, const void* kpool, const void* vpool, const int* block_tables, int max_blocks,
