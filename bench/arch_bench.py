@@ -263,7 +263,7 @@ def gifetar_kernel_table(width, dev, hbm):
         nbytes = B * (ctx0 + q) * G * (2 * D + V) * 2 + T * H * (2 * D + V) * 2
         pairs = B * (ctx0 + q) if q == 1 else (ctx0 + q) * (ctx0 + q + 1) // 2
         flops = 2 * 2 * H * (D + V) * pairs
-        args = (H, D ** -0.5, 50.0, 0.1, 1024.0, 0.7, 1e-5, 0.2, bf)
+        args = (H, D ** -0.5, 30.0, 0.1, 1024.0, 0.7, 1e-5, 0.2, bf)
         ms = timed(lambda: O.diff_attention(u, kp, vp, meta, *args))
         add(f"diff_attention {phase}", ms, nbytes, flops=flops)
         ms = timed(lambda: O.paged_kv_append(u, H * 2 * D, (H + G) * 2 * D, kp, vp, meta))

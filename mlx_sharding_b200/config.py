@@ -376,10 +376,10 @@ def _gifetar_flat(d: Dict[str, Any]) -> Dict[str, Any]:
 def gifetar_config(width=2048, vocab=32000, layers=8, heads=16, kv_heads=4, dim=64, vdim=128, experts=16, top=2, expert_ff=1024,
                    **overrides) -> Dict[str, Any]:
     """A Gifetar config.json with layer sizes that resemble a real model: ``layers`` x (differential attention + mixture of experts)."""
-    att = dict(diff=0.8, dim=dim, heads=heads, kv_heads=kv_heads, q_temp=dict(coef=0.1, every=1024), scale=dim ** -0.5, softcap=50.0, vdim=vdim)
+    att = dict(diff=0.8, dim=dim, heads=heads, kv_heads=kv_heads, q_temp=dict(coef=0.1, every=1024), scale=dim ** -0.5, softcap=30.0, vdim=vdim)
     moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff))
     d = dict(architecture="Gifetar", layers=[dict(type="attention", mixer=dict(att), mlp=dict(moe)) for _ in range(layers)],
-             norm=dict(eps=1e-5), residual_mult=0.5, vocab=vocab, width=width)
+             norm=dict(eps=1e-5), residual_mult=0.7, vocab=vocab, width=width)
     d.update(overrides)
     return d
 

@@ -131,35 +131,77 @@ __global__ void diff_attention_kernel(DiffAttnArgs a) {
   const int jbeg = blockIdx.z * a.chunk, jend = (int)min((long long)pos + 1, (long long)jbeg + a.chunk);
   constexpr int E = 16 / (int)sizeof(AT);
   const bool vec = D2 % E == 0 && V % E == 0;
+  // VEC: each thread keeps up to kPrefetch 16-byte chunks of the NEXT tile in registers while the current one is scored; what does not
+  // fit is fetched when the tile is staged.  Chunk id = row * cpr + column (keys first, then values).  The block-table entries of this
+  // CTA's key range sit in shared memory, so a chunk's address does not wait for another global load.
+  constexpr int kPrefetch = VEC ? 8 : 1;
+  uint4 pre[kPrefetch];
+  const int cpr = (D2 + V) / E, kc = D2 / E, nthr = blockDim.x;
+  const unsigned cpr_inv = (unsigned)((0x100000000ull + cpr - 1) / cpr);          // id / cpr == umulhi(id, cpr_inv) for id < 2^16
+  int* bts = reinterpret_cast<int*>(vs + kDiffTile * V);
+  const int pg0 = jbeg / a.page;
+  const bool tile_in_page = a.page % kDiffTile == 0;                               // jbeg is a multiple of the tile
+  auto tile_row0 = [&](int j0) -> long long { return ((long long)bts[j0 / a.page - pg0] * a.G + g) * a.page + j0 % a.page; };
+  auto chunk_src = [&](long long row0, int j0, int jj, int cc) -> const uint4* {
+    const long long row = tile_in_page ? row0 + jj : tile_row0(j0 + jj);
+    return reinterpret_cast<const uint4*>(cc < kc ? (const AT*)a.kpool + row * D2 + cc * E : (const AT*)a.vpool + row * V + (cc - kc) * E);
+  };
+  auto chunk_put = [&](int jj, int cc, const uint4& v) {
+    float f[E];
+    unpack16<AT>(v, f);
+    float* dst = cc < kc ? ks + jj * ldk + cc * E : vs + jj * V + (cc - kc) * E;
+#pragma unroll
+    for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+  };
+  auto prefetch = [&](int j0, int nk) {
+    const long long row0 = tile_in_page ? tile_row0(j0) : 0;
+#pragma unroll
+    for (int u = 0; u < kPrefetch; ++u) {
+      const int id = threadIdx.x + u * nthr;
+      if (id < nk * cpr) { const int jj = __umulhi((unsigned)id, cpr_inv); pre[u] = *chunk_src(row0, j0, jj, id - jj * cpr); }
+    }
+  };
+  if (VEC) {
+    if (jbeg < jend)
+      for (int i = threadIdx.x; i <= (jend - 1) / a.page - pg0; i += nthr) bts[i] = bt[pg0 + i];
+    __syncthreads();
+    if (jbeg < jend) prefetch(jbeg, min(kDiffTile, jend - jbeg));
+  }
   for (int j0 = jbeg; j0 < jend; j0 += kDiffTile) {
     __syncthreads();
     const int nk = min(kDiffTile, jend - j0);
-    for (int jj = warp; jj < nk; jj += nw) {            // each warp fetches whole rows: one block-table lookup per row
-      const int j = j0 + jj;
-      const long long base = ((long long)bt[j / a.page] * a.G + g) * a.page + j % a.page;
-      const AT* ksrc = (const AT*)a.kpool + base * D2;
-      const AT* vsrc = (const AT*)a.vpool + base * V;
-      float* kd = ks + jj * ldk;
-      float* vd = vs + jj * V;
-      if (VEC) {                                        // 16-byte stores too: rows and chunks are 16-byte aligned
-        for (int c = lane; c < (D2 + V) / E; c += 32) {
-          const bool isk = c < D2 / E;
-          const int cc = isk ? c : c - D2 / E;
-          float f[E];
-          unpack16<AT>(*reinterpret_cast<const uint4*>((isk ? ksrc : vsrc) + cc * E), f);
-          float* dst = (isk ? kd : vd) + cc * E;
+    if (VEC) {
 #pragma unroll
-          for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+      for (int u = 0; u < kPrefetch; ++u) {
+        const int id = threadIdx.x + u * nthr;
+        if (id < nk * cpr) { const int jj = __umulhi((unsigned)id, cpr_inv); chunk_put(jj, id - jj * cpr, pre[u]); }
+      }
+      if (kPrefetch * nthr < nk * cpr) {
+        const long long row0 = tile_in_page ? tile_row0(j0) : 0;
+        for (int id = kPrefetch * nthr + threadIdx.x; id < nk * cpr; id += nthr) {
+          const int jj = __umulhi((unsigned)id, cpr_inv), cc = id - jj * cpr;
+          chunk_put(jj, cc, *chunk_src(row0, j0, jj, cc));
         }
-      } else if (vec) {
-        for (int c = lane; c < D2 / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(ksrc + c * E), kd + c * E);
-        for (int c = lane; c < V / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(vsrc + c * E), vd + c * E);
-      } else {
-        for (int d = lane; d < D2; d += 32) kd[d] = ldf<AT>(ksrc + d);
-        for (int d = lane; d < V; d += 32) vd[d] = ldf<AT>(vsrc + d);
+      }
+    } else {
+      for (int jj = warp; jj < nk; jj += nw) {          // each warp fetches whole rows: one block-table lookup per row
+        const int j = j0 + jj;
+        const long long base = ((long long)bt[j / a.page] * a.G + g) * a.page + j % a.page;
+        const AT* ksrc = (const AT*)a.kpool + base * D2;
+        const AT* vsrc = (const AT*)a.vpool + base * V;
+        float* kd = ks + jj * ldk;
+        float* vd = vs + jj * V;
+        if (vec) {
+          for (int c = lane; c < D2 / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(ksrc + c * E), kd + c * E);
+          for (int c = lane; c < V / E; c += 32) unpack16<AT>(*reinterpret_cast<const uint4*>(vsrc + c * E), vd + c * E);
+        } else {
+          for (int d = lane; d < D2; d += 32) kd[d] = ldf<AT>(ksrc + d);
+          for (int d = lane; d < V; d += 32) vd[d] = ldf<AT>(vsrc + d);
+        }
       }
     }
     __syncthreads();
+    if (VEC && j0 + kDiffTile < jend) prefetch(j0 + kDiffTile, min(kDiffTile, jend - j0 - kDiffTile));
     if (!valid) continue;
     float s1 = -INFINITY, s2 = -INFINITY;
     if (lane < nk) {
@@ -296,7 +338,9 @@ int diff_attention_warps(int H, int G) {
 template <typename AT, int NPL, bool VEC>
 static cudaError_t diff_attention_launch_v(const DiffAttnArgs& a, int T, cudaStream_t s) {
   const int nw = diff_attention_warps(a.H, a.G), Rg = a.H / a.G, nb = (Rg + nw - 1) / nw;
-  const size_t smem = ((size_t)nw * 2 * a.D + (size_t)kDiffTile * (2 * a.D + (VEC ? 4 : 1)) + (size_t)kDiffTile * a.V) * sizeof(float);
+  // VEC also keeps the block-table entries of the CTA's key range: all of the table with one split, chunk / page + 2 with more
+  const size_t nbt = VEC ? (size_t)(a.nsplit == 1 ? a.max_blocks : (a.chunk / a.page + 2 < a.max_blocks ? a.chunk / a.page + 2 : a.max_blocks)) : 0;
+  const size_t smem = ((size_t)nw * 2 * a.D + (size_t)kDiffTile * (2 * a.D + (VEC ? 4 : 1)) + (size_t)kDiffTile * a.V + nbt) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   auto k = diff_attention_kernel<AT, NPL, VEC>;
   if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }

@@ -315,11 +315,12 @@ def test_wide_values_long_context(dtype, tol):
     model, sd = make_model(cfgd, "cuda", dtype)
     t = toks(300, seed=13)
     want = oracle.forward(cfgd, sd, t)
-    s, at, got = session(model, pages=21), 0, []
-    for n in [256, 2, 31, 5] + [1] * 6:
-        got.append(s.step([dict(id="r", tokens=t[at:at + n], want=list(range(n)))]))
-        at += n
-    close(torch.cat(got), want, tol * (3 if dtype == torch.bfloat16 else 1))
+    for pages, page_size in ((21, 16), (7, 64)):           # a tile of 32 keys spans two pages / lies within one
+        s, at, got = session(model, pages=pages, page_size=page_size), 0, []
+        for n in [256, 2, 31, 5] + [1] * 6:
+            got.append(s.step([dict(id="r", tokens=t[at:at + n], want=list(range(n)))]))
+            at += n
+        close(torch.cat(got), want, tol * (3 if dtype == torch.bfloat16 else 1))
 
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
