@@ -39,13 +39,14 @@ def synthetic_model_dir(name: str) -> str:
     mlx-community checkpoint), so ``mlx-sharding-api --model synthetic:llama3-8b`` serves a full-size model without a download."""
     import tempfile
 
-    from ..config import deepseek_v2_lite_config, gemma2_9b_config, llama3_8b_config
+    from ..config import deepseek_v2_lite_config, gemma2_9b_config, gifetar_config, llama3_8b_config
 
     tiny = lambda: dict(model_type="llama", vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
                         num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, rope_theta=10000.0,
                         max_position_embeddings=512, tie_word_embeddings=False)
+    tiny_gifetar = lambda: gifetar_config(width=64, vocab=320, layers=3, heads=4, kv_heads=2, dim=16, vdim=24, experts=4, top=2, expert_ff=32)
     canned = {"deepseek-v2-lite": deepseek_v2_lite_config, "llama3-8b": llama3_8b_config, "gemma2-9b": gemma2_9b_config,
-              "tiny-llama": tiny}
+              "tiny-llama": tiny, "gifetar": gifetar_config, "tiny-gifetar": tiny_gifetar}
     if name not in canned:
         raise FileNotFoundError(f"unknown synthetic model '{name}' (known: {sorted(canned)})")
     d = _SYNTH_DIRS.get(name)
@@ -58,7 +59,7 @@ def synthetic_model_dir(name: str) -> str:
             json.dump(cfg, f)
         with open(os.path.join(d, "synthetic.json"), "w") as f:
             json.dump({"name": name, "seed": 1}, f)
-        write_byte_tokenizer(d, vocab_size=min(int(cfg["vocab_size"]), 4096))
+        write_byte_tokenizer(d, vocab_size=min(int(cfg.get("vocab_size", cfg.get("vocab", 0))), 4096))
         _SYNTH_DIRS[name] = d
     return d
 

@@ -361,3 +361,16 @@ def test_cache_layout_has_pools_of_each_layers_own_sizes():
     assert [e[:4] for e in model.cache_layout()] == [("paged_kv", 2, 16, 12), ("paged_kv", 1, 32, 40), ("paged_kv", 3, 12, 10), ("paged_kv", 1, 16, 160)]
     kv = StageExecutor(model, 4, 16).kv
     assert kv.num_slots == 0 and kv.k[1].shape == (4, 1, 16, 32) and kv.v[3].shape == (4, 1, 16, 160)
+
+
+@pytest.mark.timeout(300)
+def test_command_line_generation(tmp_path):
+    """``generate.py`` on a synthetic model of the design: tokenizer, engine, sampler and the printed statistics."""
+    import subprocess
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(repo, "generate.py"), "--model", "synthetic:tiny-gifetar", "--prompt", "hello", "--max_tokens", "8",
+                        "--device", "cpu", "--no_chat_template"], capture_output=True, text=True, timeout=240,
+                       env=dict(os.environ, PYTHONPATH=repo, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Generation:" in r.stdout and "tokens-per-sec" in r.stdout
