@@ -155,6 +155,39 @@ def test_ops_alone(device, dtype, tol):
 
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES)
+@pytest.mark.parametrize("experts,top,ff,rows", [(5, 2, 24, 7), (4, 1, 16, 3), (3, 3, 8, 70), (6, 2, 128, 150)])
+def test_experts_alone(experts, top, ff, rows, device, dtype, tol):
+    """Router and routed experts as ops against the oracle's feed-forward: few rows (one weight-row read per pair), many rows (sorted
+    rows, one product per expert; expert rows of 128 take the grouped tensor-core GEMM in bf16), top-1 (weight exactly 1), all experts."""
+    from mlx_sharding_b200.ops import LinearWeight
+
+    O = get_backend("b200" if device == "cuda" else "reference")
+    K = 128
+    g = torch.Generator().manual_seed(experts * 100 + rows)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    bank = lambda o, i: (rn(experts, o, i) * i ** -0.5).bfloat16()
+    wg, wu, wd, wr, br = bank(ff, K), bank(ff, K), bank(K, ff), (rn(experts, K) * 3 * K ** -0.5).bfloat16(), (0.2 * rn(experts)).bfloat16()
+    p = {"router": wr.double(), "router.b": br.double()}
+    for e in range(experts):
+        p.update({f"e{e}.gate": wg[e].double(), f"e{e}.up": wu[e].double(), f"e{e}.down": wd[e].double()})
+    mlp = dict(router=dict(experts=experts, top=top))
+    for seed in range(200):                  # bf16: inputs whose routing has no close call
+        x = torch.randn(rows, K, generator=torch.Generator().manual_seed(seed)).bfloat16()
+        gaps = []
+        want = oracle.moe_ff(x.double(), p, mlp, gaps)
+        if dtype != torch.bfloat16 or not gaps or gaps[0] > 0.08:
+            break
+    else:
+        raise AssertionError("no input without a close routing call found")
+    dev = lambda t: t.to(device=device, dtype=dtype)
+    lw = lambda t: LinearWeight(weight=dev(t).contiguous())
+    xa = dev(x)
+    idx, wt = O.softmax_topk(O.router_logits(xa, wr.float().to(device)), br.float().to(device), experts, top)
+    assert torch.allclose(wt.sum(-1).cpu(), torch.ones(rows), atol=1e-5)
+    close(O.moe_glu_experts(xa, idx, wt, lw(wg), lw(wu), lw(wd)), want, tol if dtype == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("device,dtype,tol", DEVICES)
 def test_first_tokens_and_single_token(device, dtype, tol):
     cfgd = make_cfg(STACK)
     model, sd = make_model(cfgd, device, dtype)
