@@ -171,11 +171,11 @@ def test_experts_alone(experts, top, ff, rows, device, dtype, tol):
     for e in range(experts):
         p.update({f"e{e}.gate": wg[e].double(), f"e{e}.up": wu[e].double(), f"e{e}.down": wd[e].double()})
     mlp = dict(router=dict(experts=experts, top=top))
-    for seed in range(200):                  # bf16: inputs whose routing has no close call
+    for seed in range(200):                  # the router sees the same bf16-exact inputs as the oracle: only a near-tie could flip a choice
         x = torch.randn(rows, K, generator=torch.Generator().manual_seed(seed)).bfloat16()
         gaps = []
         want = oracle.moe_ff(x.double(), p, mlp, gaps)
-        if dtype != torch.bfloat16 or not gaps or gaps[0] > 0.08:
+        if not gaps or gaps[0] > 1e-3:
             break
     else:
         raise AssertionError("no input without a close routing call found")
