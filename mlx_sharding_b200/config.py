@@ -21,7 +21,7 @@ MODEL_REMAPPING = {
     "mistral": "llama",  # reference utils.py:15
 }
 
-SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn", "gusolorn", "gifetar")
+SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn", "gusolorn", "gifetar", "gokapel")
 
 
 @dataclass(frozen=True)
@@ -151,6 +151,9 @@ class ModelConfig:
     logit_scale: float = 1.0
     # gifetar: every sublayer's (normed) output enters the residual stream times this factor
     residual_mult: float = 1.0
+    # gokapel: number of residual streams (hyper-connections) and the factor on the embedding rows
+    streams: int = 1
+    embedding_scale: float = 1.0
     # quantisation (mlx affine) + sharding
     quantization: Optional[Dict[str, int]] = None
     start_layer: Optional[int] = None
@@ -167,6 +170,8 @@ class ModelConfig:
             d = _gusolorn_flat(d)
         elif "model_type" not in d and str(d.get("architecture", "")).lower() == "gifetar":
             d = _gifetar_flat(d)
+        elif "model_type" not in d and str(d.get("architecture", "")).lower() == "gokapel":
+            d = _gokapel_flat(d)
         mt = d.get("model_type", "llama")
         if mt == "phi-msft":
             raise ValueError(
@@ -380,6 +385,76 @@ def gifetar_config(width=2048, vocab=32000, layers=8, heads=16, kv_heads=4, dim=
     moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff))
     d = dict(architecture="Gifetar", layers=[dict(type="attention", mixer=dict(att), mlp=dict(moe)) for _ in range(layers)],
              norm=dict(eps=1e-5), residual_mult=0.7, vocab=vocab, width=width)
+    d.update(overrides)
+    return d
+
+
+def _gokapel_flat(d: Dict[str, Any]) -> Dict[str, Any]:
+    """Gokapel's nested config.json (``layers`` = list of {type, mixer, mlp[, weights_of]}; ``norm.eps``; ``residual_mult``; ``streams``;
+    ``embedding.scale``; ``vocab``; ``width``) -> the flat fields of :class:`ModelConfig`.  Mixers: ``channel_delta`` (heads, kv_heads, dim,
+    vdim, conv) and ``parallel`` (left = attention: heads, kv_heads, dim, vdim, scale, optional rot.{base, dims}, optional mask.size;
+    right = minGRU: width; left_scale, right_scale).  Feed-forwards: ``dense`` (ff), ``moe`` (router.{experts, top, groups.{count, keep}},
+    expert.ff, optional shared.ff) or none.  ``weights_of: j`` = the layer runs with layer ``j``'s tensors and a cache of its own.  Every
+    size is read from the file."""
+    layers = []
+    for L in d["layers"]:
+        ent = dict(type=str(L["type"]), mixer=dict(L["mixer"]), mlp=(dict(L["mlp"]) if L.get("mlp") else None))
+        if L.get("weights_of") is not None:
+            ent["weights_of"] = int(L["weights_of"])
+        layers.append(ent)
+    for i, L in enumerate(layers):
+        m = L["mixer"]
+        if L["type"] not in ("channel_delta", "parallel"):
+            raise ValueError(f"Gokapel: unknown mixer type '{L['type']}'")
+        if L["mlp"] is not None and L["mlp"].get("kind", "dense") not in ("dense", "moe"):
+            raise ValueError(f"Gokapel: unknown feed-forward kind '{L['mlp'].get('kind')}'")
+        att = m if L["type"] == "channel_delta" else m["left"]
+        if int(att["heads"]) % int(att["kv_heads"]) != 0:
+            raise ValueError(f"Gokapel layer {i}: heads must be a multiple of kv_heads")
+        if L["type"] == "parallel" and int((att.get("rot") or {}).get("dims", 0)) % 2 != 0 or \
+                L["type"] == "parallel" and int((att.get("rot") or {}).get("dims", 0)) > int(att["dim"]):
+            raise ValueError(f"Gokapel layer {i}: rot.dims must be even and at most dim")
+        if L["mlp"] is not None and L["mlp"].get("kind", "dense") == "moe":
+            r = L["mlp"]["router"]
+            ng = int((r.get("groups") or {}).get("count", 1))
+            keep = int((r.get("groups") or {}).get("keep", ng))
+            if int(r["experts"]) % ng != 0 or not (1 <= keep <= ng):
+                raise ValueError(f"Gokapel layer {i}: router.groups must split the experts evenly, 1 <= keep <= count")
+            if not (1 <= int(r["top"]) <= keep * (int(r["experts"]) // ng)):
+                raise ValueError(f"Gokapel layer {i}: router.top must lie in 1 .. experts of the kept groups")
+        j = L.get("weights_of")
+        if j is not None:
+            src = layers[j] if 0 <= j < len(layers) and j != i else None
+            if src is None or "weights_of" in src or (src["type"], src["mixer"], src["mlp"]) != (L["type"], L["mixer"], L["mlp"]):
+                raise ValueError(f"Gokapel layer {i}: weights_of must name another layer of the same shape that owns its tensors")
+    out = {k: v for k, v in d.items() if k not in ("architecture", "layers", "norm", "vocab", "width", "residual_mult", "streams", "embedding")}
+    ff = [L["mlp"]["ff"] if L["mlp"].get("kind", "dense") == "dense" else L["mlp"]["expert"]["ff"] for L in layers if L["mlp"]]
+    heads = [int((L["mixer"] if L["type"] == "channel_delta" else L["mixer"]["left"])["heads"]) for L in layers]
+    out.update(model_type="gokapel", hidden_size=int(d["width"]), vocab_size=int(d["vocab"]), num_hidden_layers=len(layers),
+               rms_norm_eps=float(d["norm"]["eps"]), layer_specs=layers, intermediate_size=int(max(ff)) if ff else 0,
+               residual_mult=float(d.get("residual_mult", 1.0)), streams=int(d.get("streams", 1)),
+               embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), tie_word_embeddings=True,
+               num_attention_heads=max(heads) if heads else 1)
+    if out["streams"] < 1 or out["streams"] > 8:
+        raise ValueError("Gokapel: streams must lie in 1 .. 8")
+    return out
+
+
+def gokapel_config(width=2048, vocab=32000, blocks=2, heads=16, kv_heads=4, dim=128, vdim=128, ff=8192, experts=16, top=2, expert_ff=1024,
+                   block_size=1024, gru_width=None, streams=2, **overrides) -> Dict[str, Any]:
+    """A Gokapel config.json with layer sizes that resemble a real model: ``blocks`` x (gated delta rule + dense feed-forward, gated delta
+    rule + mixture of experts, attention beside minGRU + dense feed-forward, attention beside minGRU + mixture of experts)."""
+    delta = dict(conv=4, dim=dim, heads=heads, kv_heads=heads, vdim=vdim)
+    par = dict(left=dict(dim=dim, heads=heads, kv_heads=kv_heads, mask=dict(size=block_size), rot=dict(base=10000.0, dims=dim // 2),
+                         scale=dim ** -0.5, vdim=vdim), left_scale=0.6, right=dict(width=gru_width or width), right_scale=0.5)
+    moe = dict(kind="moe", router=dict(experts=experts, top=top, groups=dict(count=4, keep=2)), expert=dict(ff=expert_ff), shared=dict(ff=expert_ff))
+    dense = dict(kind="dense", ff=ff)
+    layers = []
+    for _ in range(blocks):
+        layers += [dict(type="channel_delta", mixer=dict(delta), mlp=dict(dense)), dict(type="channel_delta", mixer=dict(delta), mlp=dict(moe)),
+                   dict(type="parallel", mixer=dict(par), mlp=dict(dense)), dict(type="parallel", mixer=dict(par), mlp=dict(moe))]
+    d = dict(architecture="Gokapel", embedding=dict(scale=1.0), layers=layers, norm=dict(eps=1e-6), residual_mult=0.5, streams=streams,
+             vocab=vocab, width=width)
     d.update(overrides)
     return d
 

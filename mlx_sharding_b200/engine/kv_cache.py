@@ -183,13 +183,14 @@ class HybridCache(PagedKVCache):
     """Cache of a model whose layers keep different things between steps: paged pools for attention layers (any row width, one
     pool per layer: ``k[li]``; ``v[li]`` is an empty tensor when the values are read out of the key rows) and per-sequence *state
     slots* for recurrent layers (``state[li]`` = dict name -> ``[num_slots, ...]`` tensor).  ``layout`` lists the local layers:
-    ``("paged", row_width, dtype)``, ``("paged_kv", kv_heads, d_k, d_v, dtype)`` (separate key and value pools ``[pages, kv_heads, page,
-    d]``, the geometry of :class:`PagedKVCache`, with sizes of the layer's own), ``("state", {name: (shape, dtype)})`` or ``("alias", j)`` (the layer keeps nothing of its own and
+    ``("paged", row_width, dtype)``, ``("paged_kv", kv_heads, d_k, d_v, dtype[, {name: (shape, dtype)}])`` (separate key and value pools ``[pages, kv_heads, page,
+    d]``, the geometry of :class:`PagedKVCache`, with sizes of the layer's own; the optional dict adds state tensors for a recurrence
+    that runs beside the attention in the same layer), ``("state", {name: (shape, dtype)})`` or ``("alias", j)`` (the layer keeps nothing of its own and
     reads local layer ``j``'s pool, which comes earlier in the list: cross-layer sharing of cached rows).  Pages and slots are managed on the host by
     :class:`SequenceTable`; the step metadata carries block tables and slot ids."""
 
     def __init__(self, layout, num_pages: int, page_size: int, num_slots: int, device="cpu"):
-        if not any(ent[0] == "state" for ent in layout):
+        if not any(ent[0] == "state" or (ent[0] == "paged_kv" and len(ent) > 5 and ent[5]) for ent in layout):
             num_slots = 0                  # no recurrent layer: sequences hold pages only, the engine hands out no slots
         self.num_layers, self.num_pages, self.page_size, self.num_slots = len(layout), num_pages, page_size, num_slots
         self.kv_heads, self.d_k, self.d_v = 1, 0, 0
@@ -206,10 +207,12 @@ class HybridCache(PagedKVCache):
                 self.v.append(torch.empty(0, dtype=ent[2], device=device))
                 self.state.append(None)
             elif ent[0] == "paged_kv":
-                _, heads, dk, dv, dt = ent
+                _, heads, dk, dv, dt = ent[:5]
                 self.k.append(torch.zeros(num_pages, heads, page_size, dk, dtype=dt, device=device))
                 self.v.append(torch.zeros(num_pages, heads, page_size, dv, dtype=dt, device=device))
-                self.state.append(None)
+                # a layer that runs attention BESIDE a recurrence keeps both: pools and, as an optional sixth entry, state tensors
+                extra = ent[5] if len(ent) > 5 else None
+                self.state.append({n: torch.zeros(num_slots, *shape, dtype=sdt, device=device) for n, (shape, sdt) in extra.items()} if extra else None)
             else:
                 self.k.append(None)
                 self.v.append(None)

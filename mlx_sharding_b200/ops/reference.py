@@ -498,10 +498,12 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: Optional[torch.T
 
 
 def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
-    """``act(x @ W^T + W.bias)`` for any shape / float dtype (fp32 accumulate; ``act``: none | gelu_erf)."""
+    """``act(x @ W^T + W.bias)`` for any shape / float dtype (fp32 accumulate; ``act``: none | gelu_erf | relu2 = ``max(., 0)^2``)."""
     y = linear(x, W, out_dtype=torch.float32)
     if act == "gelu_erf":
         y = F.gelu(y)
+    elif act == "relu2":
+        y = torch.relu(y) ** 2
     elif act != "none":
         raise NotImplementedError(act)
     return y.to(out_dtype)
@@ -718,5 +720,193 @@ def moe_glu_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wg: Lin
             continue
         xe = x[tok].float()
         h = silu_glu(xe @ Wg.weight[e].float().t(), xe @ Wu.weight[e].float().t(), x.dtype)
+        y.index_add_(0, tok, (h.float() @ Wd.weight[e].float().t()) * w[tok, slot].float()[:, None])
+    return y
+
+
+# ---- several residual streams mixed per sublayer with dynamic-tanh norms, gated delta rule with per-channel decays, grouped-query
+# ---- attention inside fixed blocks of positions with a sink, minGRU, group-limited softmax router, squared-ReLU experts
+def relu2_(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0)^2`` in place."""
+    return x.copy_((torch.relu(x.float()) ** 2).to(x.dtype))
+
+
+def stream_embed(table: torch.Tensor, ids: torch.Tensor, scale: float, streams: int) -> torch.Tensor:
+    """``streams`` equal copies of ``table[ids] * scale``: the fp32 residual streams ``[T, streams, width]`` at the start of a stack."""
+    x = table[ids.long()].float() * float(scale)
+    return x[:, None, :].repeat(1, int(streams), 1).contiguous()
+
+
+def dyt_cast(x: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Dynamic tanh in the place of a norm: ``tanh(alpha x) * w + b`` (no row statistics; fp32 arithmetic)."""
+    return (torch.tanh(float(alpha) * x.float()) * w.float() + b.float()).to(out_dtype)
+
+
+def hyper_step_(xs: torch.Tensor, y: Optional[torch.Tensor], y2: Optional[torch.Tensor], gate: Optional[torch.Tensor], ls: Optional[torch.Tensor],
+                mix: Optional[torch.Tensor], out_w: Optional[torch.Tensor], mult: float, in_w: torch.Tensor, alpha: float, w: torch.Tensor,
+                b: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+    """Residual step over several streams ``xs`` fp32 ``[T, S, width]`` (in place) and the read for the sublayer that follows.
+    With ``r = (y + y2) * ls * sigmoid(gate)`` (``y2``, ``ls``, ``gate`` optional: a second branch, a per-channel layer scale, gate
+    logits per element): ``xs[:, t] <- sum_s mix[s, t] xs[:, s] + mult * out_w[t] * r`` for all ``t`` at once; then returns
+    ``dyt(sum_s in_w[s] xs[:, s])`` in the activation dtype.  ``y is None``: only the read (the first sublayer of a stack)."""
+    if y is not None:
+        r = y.float()
+        if y2 is not None:
+            r = r + y2.float()
+        if ls is not None:
+            r = r * ls.float()
+        if gate is not None:
+            r = r * torch.sigmoid(gate.float())
+        new = torch.einsum("st,nsw->ntw", mix.float(), xs) + float(mult) * out_w.float()[None, :, None] * r[:, None, :]
+        xs.copy_(new)
+    return dyt_cast(torch.einsum("s,nsw->nw", in_w.float(), xs), alpha, w, b, act_dtype)
+
+
+def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, state: torch.Tensor,
+               meta: BatchMeta, heads: int, kv_heads: int, dim: int, vdim: int, q_scale: float, unit_eps: float = 1e-6) -> torch.Tensor:
+    """Gated delta rule with one decay per head and key channel (fp32), per head ``h`` with query / key head ``h // (heads / kv_heads)``:
+    ``q, k`` made unit vectors (``x / sqrt(sum x^2 + unit_eps)``; ``q`` times ``q_scale``), ``b = sigmoid(beta_h)``,
+    ``g = exp(-exp(A_log_h) softplus(dt + dt_bias))`` (``[dim]``), then ``S <- g[:, None] S``, ``u = b (v - S^T k)``, ``S <- S + k u^T``,
+    ``o = S^T q``.  ``qkv`` columns ``[q: kv_heads*dim | k: kv_heads*dim | v: heads*vdim]`` (after the short convolution), ``beta``
+    ``[T, heads]`` raw, ``dt`` ``[T, heads*dim]`` raw; ``state`` ``[slots, heads, dim, vdim]`` fp32.  Returns fp32 ``[T, heads*vdim]``."""
+    T, H, G, D, V = qkv.shape[0], heads, kv_heads, dim, vdim
+    q = qkv[:, :G * D].float().view(T, G, D)
+    k = qkv[:, G * D:2 * G * D].float().view(T, G, D)
+    v = qkv[:, 2 * G * D:2 * G * D + H * V].float().view(T, H, V)
+    q = (q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * q_scale).repeat_interleave(H // G, 1)
+    k = (k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(H // G, 1)
+    bt = torch.sigmoid(beta[:, :H].float())
+    g = torch.exp(-torch.exp(A_log.float()).view(1, H, 1) * F.softplus(dt[:, :H * D].float() + dt_bias.float(), threshold=30.0).view(T, H, D))
+    o = torch.empty(T, H, V, dtype=torch.float32, device=qkv.device)
+    for s, e, c0, slot in _seq_ranges(meta):
+        if e == s:
+            continue
+        S = state[slot].clone() if c0 > 0 else torch.zeros_like(state[slot])
+        for t in range(s, e):
+            S = g[t][:, :, None] * S
+            u = bt[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
+            S = S + k[t][:, :, None] * u[:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        state[slot] = S
+    return o.view(T, H * V)
+
+
+def qk_norm_rope_append(rows: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, heads: int, dim: int, qn_w: torch.Tensor, kn_w: torch.Tensor,
+                        eps: float, inv_freq: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, meta: BatchMeta) -> torch.Tensor:
+    """Attention prologue on a fused projection's rows ``[.. q: heads*dim .. k: G*dim .. v: G*dv ..]``: per head ``x / sqrt(mean(x^2) + eps)
+    * w`` on queries and keys (weights ``[dim]`` shared by the heads), then adjacent pairs ``(2i, 2i+1)`` of the first ``2 len(inv_freq)``
+    entries turn by ``position * inv_freq[i]``; keys and (untouched) values go to the pools ``[pages, G, page, d]`` at
+    ``meta.slot_mapping``.  Returns the queries fp32 ``[T, heads, dim]``."""
+    P, G, page, dk = kpool.shape
+    dv = vpool.shape[3]
+    T = rows.shape[0]
+    nrm = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    q = nrm(rows[:, q_col0:q_col0 + heads * dim].float().view(T, heads, dim), qn_w)
+    k = nrm(rows[:, k_col0:k_col0 + G * dk].float().view(T, G, dk), kn_w)
+    if inv_freq is not None and inv_freq.numel():
+        q, k = _rot_pairs(q, meta.positions, inv_freq), _rot_pairs(k, meta.positions, inv_freq)
+    slot = meta.slot_mapping.long()
+    pg, off = slot // page, slot % page
+    kpool[pg, :, off] = k.to(kpool.dtype)
+    vpool[pg, :, off] = rows[:, v_col0:v_col0 + G * dv].reshape(T, G, dv).to(vpool.dtype)
+    return q.contiguous()
+
+
+def sink_attention(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, sink: Optional[torch.Tensor], meta: BatchMeta, scale: float,
+                   block: int = 0, window: int = 0, out_mult: float = 1.0, out_dtype: torch.dtype = torch.float32,
+                   out: Optional[torch.Tensor] = None, out_col0: int = 0) -> torch.Tensor:
+    """Causal grouped-query attention over paged keys / values.  ``q`` ``[T, H, d]`` (normed and rotated), pools ``[pages, G, page, d]`` /
+    ``[pages, G, page, dv]``; head ``h`` reads key / value head ``h // (H / G)``.  The query at position ``i`` sees keys ``j <= i`` with
+    ``floor(j / block) == floor(i / block)`` (``block > 0``: blocks counted from position 0 of the sequence) and ``i - j < window``
+    (``window > 0``).  ``p_j = exp(s_j) / (exp(sink_h) + sum exp(s))`` (``sink=None``: the ordinary softmax).  The result times
+    ``out_mult`` goes to ``out[:, out_col0 : out_col0 + H * dv]`` (a fresh ``[T, H * dv]`` tensor by default), which is returned."""
+    T, H, D = q.shape
+    P, G, page, _ = kpool.shape
+    dv, rep = vpool.shape[3], H // G
+    res = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+    bt = meta.block_tables.long()
+    qf = q.float()
+    for b, (s, e, c0, _) in enumerate(_seq_ranges(meta)):
+        n = c0 + (e - s)
+        idx = torch.arange(n, device=q.device)
+        pg, off = bt[b, idx // page], idx % page
+        K = kpool[pg, :, off].float().repeat_interleave(rep, 1)                           # [n, H, d]
+        V = vpool[pg, :, off].float().repeat_interleave(rep, 1)                           # [n, H, dv]
+        sc = torch.einsum("thd,nhd->thn", qf[s:e], K) * scale
+        qpos = (c0 + torch.arange(e - s, device=q.device))[:, None]
+        mask = idx[None, :] > qpos
+        if block > 0:
+            mask = mask | ((idx[None, :] // block) != (qpos // block))
+        if window > 0:
+            mask = mask | (idx[None, :] <= qpos - window)
+        sc = sc.masked_fill(mask[:, None, :], float("-inf"))
+        if sink is None:
+            p = torch.softmax(sc, -1)
+        else:
+            sk = sink.float().view(1, H, 1).expand(e - s, H, 1)
+            p = torch.softmax(torch.cat([sc, sk], -1), -1)[..., :n]
+        res[s:e] = torch.einsum("thn,nhv->thv", p, V)
+    res = res.view(T, H * dv) * out_mult
+    if out is None:
+        return res.to(out_dtype)
+    out[:, out_col0:out_col0 + H * dv] = res.to(out.dtype)
+    return out
+
+
+def mingru_scan(rows: torch.Tensor, z_col0: int, x_col0: int, g_col0: int, width: int, state: torch.Tensor, meta: BatchMeta,
+                out_mult: float = 1.0, out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None, out_col0: int = 0) -> torch.Tensor:
+    """Element-wise gated recurrence whose gates read the current token only (fp32): ``z = sigmoid(rows[z])``, candidate ``c = u + 1/2``
+    where ``u = rows[x] >= 0`` and ``sigmoid(u)`` below, ``S <- (1 - z) S + z c``; the result ``S * silu(rows[g]) * out_mult`` goes to
+    ``out[:, out_col0 : out_col0 + width]`` (a fresh tensor by default).  ``rows``: a fused projection's output (biases added);
+    ``state`` ``[slots, width]`` fp32."""
+    T = rows.shape[0]
+    z = torch.sigmoid(rows[:, z_col0:z_col0 + width].float())
+    u = rows[:, x_col0:x_col0 + width].float()
+    c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    gt = F.silu(rows[:, g_col0:g_col0 + width].float())
+    res = torch.empty(T, width, dtype=torch.float32, device=rows.device)
+    for s, e, c0, slot in _seq_ranges(meta):
+        if e == s:
+            continue
+        S = state[slot].clone() if c0 > 0 else torch.zeros_like(state[slot])
+        for t in range(s, e):
+            S = (1.0 - z[t]) * S + z[t] * c[t]
+            res[t] = S * gt[t]
+        state[slot] = S
+    res = res * out_mult
+    if out is None:
+        return res.to(out_dtype)
+    out[:, out_col0:out_col0 + width] = res.to(out.dtype)
+    return out
+
+
+def group_softmax_topk(z: torch.Tensor, correction: Optional[torch.Tensor], num_experts: int, top: int, n_groups: int = 1,
+                       keep_groups: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router on fp32 logits ``z[:, :num_experts]``: scores ``s = softmax(z)`` over all experts; the choice is made on ``s + correction``:
+    with ``n_groups > 1`` the experts form equal runs of neighbours, a group's value is its largest choice score, and only experts of the
+    ``keep_groups`` best groups can be chosen (the others count as minus infinity); the ``top`` largest win (ties: lowest id).  Weights =
+    the chosen experts' plain ``s``.  Returns ``(idx int32 [T, top], w fp32 [T, top])``."""
+    s = torch.softmax(z[:, :num_experts].float(), -1)
+    c = s + correction.float() if correction is not None else s.clone()
+    if n_groups > 1 and keep_groups < n_groups:
+        gs = c.view(-1, n_groups, num_experts // n_groups).max(-1).values
+        best = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep_groups]
+        ok = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, best, True)
+        c = c.masked_fill(~ok.repeat_interleave(num_experts // n_groups, 1), float("-inf"))
+    order = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
+    return order.to(torch.int32), torch.gather(s, 1, order)
+
+
+def moe_relu2_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wu: LinearWeight, Wd: LinearWeight) -> torch.Tensor:
+    """``y[t] = sum_j w[t,j] expert_{idx[t,j]}(x[t])`` with experts ``W_down relu(W_up x)^2``: the router weight scales the expert's
+    OUTPUT.  Banks ``Wu`` ``[E, F, K]``, ``Wd`` ``[E, K, F]``.  Returns fp32 ``[T, K]``."""
+    T, k = idx.shape
+    y = torch.zeros(T, Wd.weight.shape[1], dtype=torch.float32, device=x.device)
+    il = idx.long()
+    for e in range(Wu.weight.shape[0]):
+        tok, slot = torch.where(il == e)
+        if tok.numel() == 0:
+            continue
+        h = (torch.relu(x[tok].float() @ Wu.weight[e].float().t()) ** 2).to(x.dtype)
         y.index_add_(0, tok, (h.float() @ Wd.weight[e].float().t()) * w[tok, slot].float()[:, None])
     return y

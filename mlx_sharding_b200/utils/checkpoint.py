@@ -39,14 +39,16 @@ def synthetic_model_dir(name: str) -> str:
     mlx-community checkpoint), so ``mlx-sharding-api --model synthetic:llama3-8b`` serves a full-size model without a download."""
     import tempfile
 
-    from ..config import deepseek_v2_lite_config, gemma2_9b_config, gifetar_config, llama3_8b_config
+    from ..config import deepseek_v2_lite_config, gemma2_9b_config, gifetar_config, gokapel_config, llama3_8b_config
 
     tiny = lambda: dict(model_type="llama", vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
                         num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, rope_theta=10000.0,
                         max_position_embeddings=512, tie_word_embeddings=False)
     tiny_gifetar = lambda: gifetar_config(width=64, vocab=320, layers=3, heads=4, kv_heads=2, dim=16, vdim=24, experts=4, top=2, expert_ff=32)
+    tiny_gokapel = lambda: gokapel_config(width=64, vocab=320, blocks=1, heads=4, kv_heads=2, dim=16, vdim=24, ff=96, experts=4, top=2, expert_ff=32,
+                                          block_size=24, gru_width=40)
     canned = {"deepseek-v2-lite": deepseek_v2_lite_config, "llama3-8b": llama3_8b_config, "gemma2-9b": gemma2_9b_config,
-              "tiny-llama": tiny, "gifetar": gifetar_config, "tiny-gifetar": tiny_gifetar}
+              "tiny-llama": tiny, "gifetar": gifetar_config, "tiny-gifetar": tiny_gifetar, "gokapel": gokapel_config, "tiny-gokapel": tiny_gokapel}
     if name not in canned:
         raise FileNotFoundError(f"unknown synthetic model '{name}' (known: {sorted(canned)})")
     d = _SYNTH_DIRS.get(name)
@@ -96,11 +98,11 @@ def key_in_shard(key: str, spec: ShardSpec, tied_embeddings: bool = False, model
     """True if checkpoint tensor ``key`` belongs to stage ``spec`` (half-layer boundaries included)."""
     if "rotary_emb.inv_freq" in key:
         return False
-    if model_type in ("perelorn", "gusolorn", "gifetar"):       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
+    if model_type in ("perelorn", "gusolorn", "gifetar", "gokapel"):       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
         m = re.match(r"l(\d+)\.", key)
         if m:
             return spec.owns_layer(int(m.group(1)))
-        return spec.is_last if key in ("final.norm", "final.norm.b", "head") else True
+        return spec.is_last if key in ("final.norm", "final.norm.b", "final.norm.alpha", "head") else True
     m = _LAYER_RE.match(key)
     if m:
         i = int(m.group(1))
@@ -258,6 +260,9 @@ def random_state_dict(cfg: ModelConfig, spec: Optional[ShardSpec] = None, dtype=
         return
     if cfg.model_type == "gifetar":
         yield from _gifetar_random(cfg, gen, dtype, device, seed)
+        return
+    if cfg.model_type == "gokapel":
+        yield from _gokapel_random(cfg, gen, dtype, device, seed)
         return
     H = cfg.hidden_size
     q = quantization
@@ -521,3 +526,79 @@ def _gifetar_random(cfg: ModelConfig, gen, dtype, device, seed: int):
             yield p + "mlp.router.b", small(E)
     yield "final.norm", vec(W)
     yield "final.norm.b", small(W)
+
+
+def _gokapel_random(cfg: ModelConfig, gen, dtype, device, seed: int, ranks=(32, 32)):
+    """Random-init Gokapel tensors (checkpoint names and shapes of that design: dynamic-tanh norms with weight, bias and a scalar, layer
+    scales, gated-residual matrices, stream in / out / mix weights, short convolutions, low-rank decay and gate maps, per-expert matrices,
+    router with correction; the LM head is the embedding table).  A layer with ``weights_of`` has no tensors.  ``ranks``: inner sizes of
+    the two low-rank maps (tensor shapes, not configuration)."""
+    gen.manual_seed(seed * 1000003 + 41)
+    W, S = cfg.hidden_size, int(cfg.streams)
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
+    lin = lambda o, i, gain=1.0: (rn(o, i) * gain / (i ** 0.5)).to(dtype)
+    vec = lambda n: (1.0 + 0.1 * rn(n)).to(dtype)
+    small = lambda n, std=0.2: (std * rn(n)).to(dtype)
+
+    def norm(name):
+        yield name, vec(W)
+        yield name + ".b", small(W)
+        yield name + ".alpha", (0.6 + 0.1 * rn(1))[0].to(dtype)
+
+    yield "embed", rn(cfg.vocab_size, W, std=0.5).to(dtype)
+    for i, L in enumerate(cfg.layer_specs):
+        if L.get("weights_of") is not None:
+            continue
+        p, m, mlp = f"l{i}.", L["mixer"], L["mlp"]
+        for q in (1, 2) if mlp else (1,):
+            yield from norm(f"{p}norm{q}")
+            yield f"{p}ls{q}", vec(W)
+            yield f"{p}hc{q}.in", (1.0 / S + 0.1 * rn(S)).to(dtype)
+            yield f"{p}hc{q}.out", vec(S)
+            yield f"{p}hc{q}.mix", (0.9 * torch.eye(S, device=device) + 0.1 * rn(S, S)).to(dtype)
+            yield f"{p}rg{q}", lin(W, W)
+            yield f"{p}rg{q}.b", small(W)
+        if L["type"] == "channel_delta":
+            H, G, D, V, K = (int(m[k]) for k in ("heads", "kv_heads", "dim", "vdim", "conv"))
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * V)):
+                yield p + "mix." + n, lin(rows, W)
+                yield p + "mix." + n + ".conv", (0.5 * rn(rows, K)).to(dtype)
+            yield p + "mix.b", lin(H, W)
+            yield p + "mix.A_log", torch.log(torch.rand(H, generator=gen, device=device) * 1.5 + 0.05).to(dtype)
+            yield p + "mix.norm", vec(V)
+            yield p + "mix.a1", lin(ranks[0], W)
+            yield p + "mix.a2", lin(H * D, ranks[0])
+            yield p + "mix.dt_bias", (rn(H * D) - 1.0).to(dtype)
+            yield p + "mix.g1", lin(ranks[1], W)
+            yield p + "mix.g2", lin(H * V, ranks[1])
+            yield p + "mix.o", lin(W, H * V)
+        else:
+            a, r = m["left"], m["right"]
+            H, G, D, V, R = int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"]), int(r["width"])
+            yield p + "mix.left.q", lin(H * D, W)
+            yield p + "mix.left.k", lin(G * D, W)
+            yield p + "mix.left.v", lin(G * V, W)
+            yield p + "mix.left.q.norm", vec(D)
+            yield p + "mix.left.k.norm", vec(D)
+            yield p + "mix.left.sink", small(H, 1.0)
+            yield p + "mix.left.o", lin(W, H * V)
+            for n in ("z", "x", "g"):
+                yield p + "mix.right." + n, lin(R, W)
+            yield p + "mix.right.z.b", small(R)
+            yield p + "mix.right.x.b", small(R)
+            yield p + "mix.right.o", lin(W, R)
+        if mlp and mlp.get("kind", "dense") == "dense":
+            yield p + "mlp.up", lin(int(mlp["ff"]), W)
+            yield p + "mlp.down", lin(W, int(mlp["ff"]))
+        elif mlp:
+            F, E = int(mlp["expert"]["ff"]), int(mlp["router"]["experts"])
+            for e in range(E):
+                yield p + f"mlp.e{e}.up", lin(F, W)
+                yield p + f"mlp.e{e}.down", lin(W, F)
+            yield p + "mlp.router", lin(E, W, 3.0)
+            yield p + "mlp.correction", small(E, 0.05)
+            if mlp.get("shared"):
+                Fs = int(mlp["shared"]["ff"])
+                yield p + "mlp.shared.up", lin(Fs, W)
+                yield p + "mlp.shared.down", lin(W, Fs)
+    yield from norm("final.norm")
