@@ -135,9 +135,11 @@ class GokapelStage(StageModel):
             if L["type"] == "channel_delta":
                 H, G, D, V = (int(m[k]) for k in ("heads", "kv_heads", "dim", "vdim"))
                 names = ("q", "k", "v")
-                parts = [(n, sd.pop(p + "mix." + n), None) for n in names] + [(n, sd.pop(p + "mix." + n), None) for n in ("b", "a1", "g1")]
-                if tuple(parts[0][1].shape[:1]) != (G * D,) or parts[2][1].shape[0] != H * V or parts[3][1].shape[0] != H:
+                qkv = [sd.pop(p + "mix." + n) for n in names]
+                if [t.shape[0] for t in qkv] != [G * D, G * D, H * V] or sd[p + "mix.b"].shape[0] != H:
                     raise ValueError(f"{p}mix: projection shapes do not fit heads / kv_heads / dim / vdim")
+                # q, k, v stay adjacent (one segment): the short convolution and the scan read them as one block of columns
+                parts = [("qkv", torch.cat(qkv), None)] + [(n, sd.pop(p + "mix." + n), None) for n in ("b", "a1", "g1")]
                 w["proj"], w["seg"] = self._fused(parts + gate_part)
                 w["conv"] = torch.cat([self._f32(sd, p + f"mix.{n}.conv") for n in names]).contiguous()
                 w["conv_b"] = torch.zeros(w["conv"].shape[0], device=dev)
@@ -204,7 +206,7 @@ class GokapelStage(StageModel):
         """Returns ``(mixer output fp32 [T, width], gate logits of the gated residual or None)``."""
         O, eps, seg = self.ops, self.cfg.rms_norm_eps, w["seg"]
         H, G, D, V = (int(m[k]) for k in ("heads", "kv_heads", "dim", "vdim"))
-        u = self.ops.linear_any(ha, w["proj"], self.dtype)                            # [q | k | v | b | a1 | g1 | rg]
+        u = self.ops.linear_any(ha, w["proj"], self.dtype)                            # [q k v | b | a1 | g1 | rg]
         C = 2 * G * D + H * V                                                        # q, k, v are adjacent: one convolution over all
         qkv = O.causal_conv_silu(u[:, :C], w["conv"], w["conv_b"], st["conv"], meta)
         dt = self._mm(self._cols(u, seg, "a1"), w["a2"], True)                        # fp32 raw step sizes [T, H * D]

@@ -497,7 +497,10 @@ def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: st
     w = W.weight
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] > 0):
-        y = C().linear(x, w, None, None, W.bias, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+        fused = act == "relu2"                      # the squared ReLU runs in the product's epilogue
+        y = C().linear(x, w, None, None, W.bias, ACT_RELU2 if fused else 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+        if fused:
+            return y
     elif out_dtype == torch.float32 and x.dtype != torch.float32:
         # odd shapes with an fp32 result (scores, residual-stream inputs): the library product of the widened operands, so that the
         # result is not rounded to bf16 on its way out
@@ -507,6 +510,8 @@ def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: st
         y = y if y.dtype == out_dtype else y.to(out_dtype)
     if act == "gelu_erf":
         return gelu_erf_(y)
+    if act == "relu2":
+        return relu2_(y)
     if act != "none":
         raise NotImplementedError(act)
     return y
@@ -773,3 +778,96 @@ def diff_attention_prefill(q, kpool, vpool, meta: BatchMeta, heads: int, scale: 
                 p = C().hy_sink_softmax(s, None, int(Rg), int(ctx0 + t0), float(scale), is32, 0, 0, float(softcap), float(temp_coef), float(temp_every))
                 A[g, c, t0 * Rg:(t0 + n) * Rg] = linear_any(p, Wv_b, torch.float32)
     return C().hy_diff_head_norm(A, int(T), int(heads), float(lam), float(eps), float(out_mult), is32)
+
+
+# ---- several residual streams with dynamic-tanh norms, gated delta rule, attention with a sink inside blocks of positions, minGRU,
+# ---- group-limited softmax router, squared-ReLU experts (``ops/csrc/streams.cu``; same functions as in ``ops/reference.py``)
+ACT_RELU2 = 4            # single-weight GEMM epilogue: max(y, 0)^2
+
+
+def relu2_(x):
+    return C().hy_relu2_(x)
+
+
+def stream_embed(table, ids, scale: float, streams: int):
+    return C().hy_stream_embed(table, ids, float(scale), int(streams))
+
+
+def dyt_cast(x, alpha: float, w, b, out_dtype):
+    one = torch.ones(1, dtype=torch.float32, device=x.device)
+    return C().hy_hyper_step_(x.view(x.shape[0], 1, x.shape[1]), None, None, None, None, None, None, 0.0, one, float(alpha), w, b, _is32(out_dtype))
+
+
+def hyper_step_(xs, y, y2, gate, ls, mix, out_w, mult: float, in_w, alpha: float, w, b, act_dtype):
+    return C().hy_hyper_step_(xs, y, y2, gate, ls, mix, out_w, float(mult), in_w, float(alpha), w, b, _is32(act_dtype))
+
+
+def delta_scan(qkv, beta, dt, dt_bias, A_log, state, meta: BatchMeta, heads: int, kv_heads: int, dim: int, vdim: int, q_scale: float,
+               unit_eps: float = 1e-6):
+    return C().hy_delta_scan(qkv, beta, dt, dt_bias, A_log, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(kv_heads), int(dim),
+                             int(vdim), float(q_scale), float(unit_eps), int(meta.max_q_len))
+
+
+def qk_norm_rope_append(rows, q_col0: int, k_col0: int, v_col0: int, heads: int, dim: int, qn_w, kn_w, eps: float, inv_freq, kpool, vpool, meta: BatchMeta):
+    return C().hy_qk_norm_rope_append(rows, int(q_col0), int(k_col0), int(v_col0), int(heads), int(dim), qn_w, kn_w, float(eps), inv_freq, kpool, vpool,
+                                      meta.slot_mapping, meta.positions)
+
+
+def sink_attention(q, kpool, vpool, sink, meta: BatchMeta, scale: float, block: int = 0, window: int = 0, out_mult: float = 1.0, out_dtype=None,
+                   out=None, out_col0: int = 0):
+    return C().hy_sink_attention(q, kpool, vpool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(block), int(window),
+                                 float(out_mult), int(meta.max_ctx_len), out, int(out_col0))
+
+
+def mingru_scan(rows, z_col0: int, x_col0: int, g_col0: int, width: int, state, meta: BatchMeta, out_mult: float = 1.0, out_dtype=None, out=None,
+                out_col0: int = 0):
+    return C().hy_mingru_scan(rows, int(z_col0), int(x_col0), int(g_col0), int(width), state, meta.cu_seqlens, meta.context_lens, _slots(meta),
+                              float(out_mult), out, int(out_col0))
+
+
+def group_softmax_topk(z, correction, num_experts: int, top: int, n_groups: int = 1, keep_groups: int = 1):
+    idx, w = C().hy_group_softmax_topk(z, correction, int(num_experts), int(top), int(n_groups), int(keep_groups))
+    return idx, w
+
+
+def moe_relu2_experts(x, idx, w, Wu: LinearWeight, Wd: LinearWeight):
+    """Routed squared-ReLU experts with the router weight on the expert's OUTPUT (applied in fp32 where the pairs are summed per token).
+    bf16 banks whose sizes fit the grouped tcgen05 GEMM: counting-sort permutation -> grouped up GEMM with the squared ReLU in its
+    epilogue -> grouped down GEMM (fp32) -> weighted sum per token.  Exact mode (fp32) and other sizes: one weight-row read per (token,
+    choice) pair (few rows; anything inside a graph capture) or one cuBLAS product per expert on the sorted rows."""
+    c = C()
+    T, k = idx.shape
+    wu, wd = Wu.weight, Wd.weight
+    E, F, K = wu.shape
+    wts = w.reshape(-1).contiguous()
+    if _tc_ok(x) and wu.dtype == torch.bfloat16 and F % 128 == 0 and K % 128 == 0:
+        offs, pair_row, xp = c.moe_permute(idx, x, E, None)
+        h = c.grouped_linear(xp, wu, None, offs, T, ACT_RELU2, False)
+        y = c.grouped_linear(h, wd, None, offs, T, 0, True)
+        return c.hy_gather_sum(y, pair_row, int(k), wts)
+    R = T * k
+    if R <= PAIR_KERNEL_MAX_ROWS or torch.cuda.is_current_stream_capturing():
+        ids = idx.reshape(-1).contiguous()
+        h = c.hy_relu2_(c.hy_expert_rows_linear(x, int(k), wu, ids, False))
+        y = c.hy_expert_rows_linear(h, 1, wd, ids, True)
+        return c.hy_gather_sum(y, None, int(k), wts)
+    flat = idx.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    pair_row = torch.empty_like(order, dtype=torch.int32)
+    pair_row[order] = torch.arange(order.numel(), device=x.device, dtype=torch.int32)
+    xp = gather_rows(x, (order // k).contiguous(), 0, K, x.dtype)
+    counts = torch.bincount(flat, minlength=E).tolist()
+    h = torch.empty(R, F, dtype=x.dtype, device=x.device)
+    r0 = 0
+    for e, n in enumerate(counts):
+        if n:
+            torch.matmul(xp[r0:r0 + n], wu[e].t(), out=h[r0:r0 + n])
+        r0 += n
+    c.hy_relu2_(h)
+    y = torch.empty(R, K, dtype=torch.float32, device=x.device)
+    r0 = 0
+    for e, n in enumerate(counts):
+        if n:
+            y[r0:r0 + n] = torch.matmul(h[r0:r0 + n], wd[e].t()).float()
+        r0 += n
+    return c.hy_gather_sum(y, pair_row, int(k), wts)

@@ -22,9 +22,9 @@ OBJ = os.path.join(HERE, "_build")
 MODULE = "_b200_C"
 SO_PATH = os.path.join(HERE, MODULE + ".so")
 
-CU_SOURCES = ["gemm_tcgen05.cu", "gemm_persistent.cu", "gemm_q_tcgen05.cu", "gemm_q_persistent.cu", "gemm_fp8.cu", "elementwise.cu", "attention.cu", "attention_prefill.cu", "mla_decode.cu", "moe.cu", "sampler.cu", "p2p.cu", "ep.cu", "hybrid.cu", "diffattn.cu"]
+CU_SOURCES = ["gemm_tcgen05.cu", "gemm_persistent.cu", "gemm_q_tcgen05.cu", "gemm_q_persistent.cu", "gemm_fp8.cu", "elementwise.cu", "attention.cu", "attention_prefill.cu", "mla_decode.cu", "moe.cu", "sampler.cu", "p2p.cu", "ep.cu", "hybrid.cu", "diffattn.cu", "streams.cu"]
 # exact-mode kernels (fp32 recurrences, rotary angles of long positions): IEEE division / exp / sincos
-NO_FAST_MATH = {"hybrid.cu", "diffattn.cu"}
+NO_FAST_MATH = {"hybrid.cu", "diffattn.cu", "streams.cu"}
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--use_fast_math",
                      "-Xptxas", "-v"]

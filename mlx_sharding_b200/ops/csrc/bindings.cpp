@@ -12,6 +12,7 @@
 #include "kernels.h"
 #include "hybrid.h"
 #include "diffattn.h"
+#include "streams.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -1178,6 +1179,170 @@ Tensor hy_diff_head_norm(const Tensor& a, int64_t T, int64_t H, double lam, doub
   return out;
 }
 
+// ---- several residual streams, gated delta rule, attention with a sink, minGRU, group-limited router (streams.cu) ----------------------
+Tensor hy_stream_embed(const Tensor& table, const Tensor& ids, double scale, int64_t S) {
+  check_act(table, "table"); check_rows(table, "table");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && S >= 1 && S <= 8, "streams: 1 .. 8");
+  const c10::cuda::CUDAGuard guard(table.device());
+  Tensor xs = torch::empty({ids.numel(), S, table.size(1)}, table.options().dtype(torch::kFloat32));
+  if (ids.numel() == 0) return xs;
+  LAUNCH_OK(b200::stream_embed_launch(table.data_ptr(), is_f32(table), table.stride(0), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (float)scale,
+                                      (int)S, (int)table.size(1), xs.data_ptr<float>(), (int)ids.numel(), cur_stream()));
+  return xs;
+}
+
+Tensor hy_hyper_step_(Tensor xs, const c10::optional<Tensor>& y, const c10::optional<Tensor>& y2, const c10::optional<Tensor>& gate,
+                      const c10::optional<Tensor>& ls, const c10::optional<Tensor>& mix, const c10::optional<Tensor>& out_w, double mult,
+                      const Tensor& in_w, double alpha, const Tensor& w, const Tensor& b, bool act_f32) {
+  check_f32c(xs, "xs"); check_f32c(in_w, "in_w"); check_f32c(w, "w"); check_f32c(b, "b");
+  TORCH_CHECK(xs.dim() == 3 && xs.size(1) >= 1 && xs.size(1) <= 8, "streams [T, S <= 8, width]");
+  const int64_t T = xs.size(0), S = xs.size(1), n = xs.size(2);
+  TORCH_CHECK(in_w.numel() == S && w.numel() == n && b.numel() == n);
+  const float *yp = nullptr, *y2p = nullptr, *lsp = nullptr, *mp = nullptr, *op = nullptr; const void* gp = nullptr; long long ldy = 0, ldy2 = 0, ldg = 0;
+  if (y.has_value()) {
+    check_rows(*y, "y");
+    TORCH_CHECK(y->is_cuda() && y->scalar_type() == torch::kFloat32 && y->size(0) == T && y->size(1) == n && mix.has_value() && out_w.has_value());
+    check_f32c(*mix, "mix"); check_f32c(*out_w, "out_w");
+    TORCH_CHECK(mix->numel() == S * S && out_w->numel() == S);
+    yp = y->data_ptr<float>(); ldy = y->stride(0); mp = mix->data_ptr<float>(); op = out_w->data_ptr<float>();
+    if (y2.has_value()) {
+      check_rows(*y2, "y2");
+      TORCH_CHECK(y2->is_cuda() && y2->scalar_type() == torch::kFloat32 && y2->size(0) == T && y2->size(1) == n);
+      y2p = y2->data_ptr<float>(); ldy2 = y2->stride(0);
+    }
+    if (gate.has_value()) {
+      check_act(*gate, "gate"); check_rows(*gate, "gate");
+      TORCH_CHECK(is_f32(*gate) == act_f32 && gate->size(0) == T && gate->size(1) == n, "gate logits [T, width] in the activation type");
+      gp = gate->data_ptr(); ldg = gate->stride(0);
+    }
+    if (ls.has_value()) { check_f32c(*ls, "ls"); TORCH_CHECK(ls->numel() == n); lsp = ls->data_ptr<float>(); }
+  }
+  const c10::cuda::CUDAGuard guard(xs.device());
+  Tensor xa = torch::empty({T, n}, xs.options().dtype(act_type(act_f32)));
+  if (T == 0) return xa;
+  LAUNCH_OK(b200::hyper_step_launch(xs.data_ptr<float>(), yp, ldy, y2p, ldy2, gp, ldg, lsp, mp, op, (float)mult, in_w.data_ptr<float>(), (float)alpha,
+                                    w.data_ptr<float>(), b.data_ptr<float>(), xa.data_ptr(), act_f32, (int)S, (int)n, (int)T, cur_stream()));
+  return xa;
+}
+
+Tensor hy_relu2_(Tensor x) {
+  check_act(x, "x"); check_rows(x, "x");
+  const c10::cuda::CUDAGuard guard(x.device());
+  if (x.size(0) == 0) return x;
+  LAUNCH_OK(b200::relu2_launch(x.data_ptr(), x.stride(0), (int)x.size(1), is_f32(x), (int)x.size(0), cur_stream()));
+  return x;
+}
+
+Tensor hy_delta_scan(const Tensor& qkv, const Tensor& beta, const Tensor& dt, const Tensor& dt_bias, const Tensor& A_log, Tensor state, const Tensor& cu,
+                     const Tensor& ctx, const Tensor& slots, int64_t H, int64_t G, int64_t Dk, int64_t V, double q_scale, double unit_eps, int64_t max_q) {
+  check_act(qkv, "qkv"); check_rows(qkv, "qkv"); check_act(beta, "beta"); check_rows(beta, "beta"); check_rows(dt, "dt"); check_f32c(dt_bias, "dt_bias");
+  check_f32c(A_log, "A_log"); check_f32c(state, "state"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
+  TORCH_CHECK(G >= 1 && H % G == 0 && qkv.size(1) >= 2 * G * Dk + H * V && beta.scalar_type() == qkv.scalar_type() && beta.size(0) == qkv.size(0) &&
+              beta.size(1) >= H && dt.is_cuda() && dt.scalar_type() == torch::kFloat32 && dt.size(0) == qkv.size(0) && dt.size(1) >= H * Dk &&
+              dt_bias.numel() == H * Dk && A_log.numel() == H);
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == Dk && state.size(3) == V, "delta-rule state [slots, heads, dim, vdim]");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor out = torch::empty({qkv.size(0), H * V}, qkv.options().dtype(torch::kFloat32));
+  if (qkv.size(0) == 0) return out;
+  LAUNCH_OK(b200::delta_scan_launch(qkv.data_ptr(), qkv.stride(0), beta.data_ptr(), beta.stride(0), dt.data_ptr<float>(), dt.stride(0), dt_bias.data_ptr<float>(),
+                                    A_log.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(), ctx.data_ptr<int>(), slots.data_ptr<int>(),
+                                    out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)G, (int)Dk, (int)V, (float)q_scale, (float)unit_eps, is_f32(qkv),
+                                    (int)max_q, cur_stream()));
+  return out;
+}
+
+// out (optional): AT [T, >= col0 + width], the result goes to its columns col0 .. col0 + width
+Tensor hy_mingru_scan(const Tensor& rows, int64_t z0, int64_t x0, int64_t g0, int64_t R, Tensor state, const Tensor& cu, const Tensor& ctx, const Tensor& slots,
+                      double out_mult, const c10::optional<Tensor>& out_, int64_t col0) {
+  check_act(rows, "rows"); check_rows(rows, "rows"); check_f32c(state, "state"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens");
+  check_i32(slots, "state_slots");
+  TORCH_CHECK(R >= 1 && z0 >= 0 && x0 >= 0 && g0 >= 0 && std::max({z0, x0, g0}) + R <= rows.size(1) && state.dim() == 2 && state.size(1) == R);
+  const c10::cuda::CUDAGuard guard(rows.device());
+  Tensor out = out_.has_value() ? *out_ : torch::empty({rows.size(0), R}, rows.options());
+  check_rows(out, "out");
+  TORCH_CHECK(out.scalar_type() == rows.scalar_type() && out.size(0) == rows.size(0) && col0 >= 0 && col0 + R <= out.size(1));
+  if (rows.size(0) == 0) return out;
+  LAUNCH_OK(b200::mingru_scan_launch(rows.data_ptr(), rows.stride(0), (int)z0, (int)x0, (int)g0, (int)R, state.data_ptr<float>(), cu.data_ptr<int>(),
+                                     ctx.data_ptr<int>(), slots.data_ptr<int>(), (float)out_mult,
+                                     static_cast<char*>(out.data_ptr()) + col0 * out.element_size(), out.stride(0), (int)slots.numel(), is_f32(rows), cur_stream()));
+  return out;
+}
+
+Tensor hy_qk_norm_rope_append(const Tensor& rows, int64_t q0, int64_t k0, int64_t v0, int64_t H, int64_t D, const Tensor& qn, const Tensor& kn, double eps,
+                              const Tensor& inv_freq, Tensor kpool, Tensor vpool, const Tensor& slot_map, const Tensor& positions) {
+  check_act(rows, "rows"); check_rows(rows, "rows"); check_f32c(qn, "q norm"); check_f32c(kn, "k norm"); check_f32c(inv_freq, "inv_freq");
+  check_i32(slot_map, "slot_mapping"); check_i32(positions, "positions");
+  TORCH_CHECK(kpool.dim() == 4 && vpool.dim() == 4 && kpool.is_contiguous() && vpool.is_contiguous() && kpool.scalar_type() == rows.scalar_type() &&
+              vpool.scalar_type() == rows.scalar_type() && kpool.size(0) == vpool.size(0) && kpool.size(1) == vpool.size(1) && kpool.size(2) == vpool.size(2) &&
+              kpool.size(3) == D, "pools [pages, kv_heads, page, d] in the activation type");
+  const int64_t T = rows.size(0), G = kpool.size(1), V = vpool.size(3), rot = 2 * inv_freq.numel();
+  TORCH_CHECK(q0 >= 0 && k0 >= 0 && v0 >= 0 && q0 + H * D <= rows.size(1) && k0 + G * D <= rows.size(1) && v0 + G * V <= rows.size(1) && rot <= D &&
+              qn.numel() == D && kn.numel() == D && slot_map.numel() >= T && positions.numel() >= T);
+  const c10::cuda::CUDAGuard guard(rows.device());
+  Tensor q = torch::empty({T, H, D}, rows.options().dtype(torch::kFloat32));
+  if (T == 0) return q;
+  LAUNCH_OK(b200::qk_norm_rope_append_launch(rows.data_ptr(), rows.stride(0), (int)q0, (int)k0, (int)v0, (int)H, (int)G, (int)D, (int)V, qn.data_ptr<float>(),
+                                             kn.data_ptr<float>(), (float)eps, inv_freq.data_ptr<float>(), (int)rot, positions.data_ptr<int>(),
+                                             slot_map.data_ptr<int>(), (int)kpool.size(2), q.data_ptr<float>(), kpool.data_ptr(), vpool.data_ptr(), is_f32(rows),
+                                             (int)T, cur_stream()));
+  return q;
+}
+
+Tensor hy_sink_attention(const Tensor& q, const Tensor& kpool, const Tensor& vpool, const c10::optional<Tensor>& sink, const Tensor& block_tables,
+                         const Tensor& positions, const Tensor& cu, double scale, int64_t block, int64_t window, double out_mult, int64_t max_ctx,
+                         const c10::optional<Tensor>& out_, int64_t col0) {
+  check_f32c(q, "q"); check_i32(block_tables, "block_tables"); check_i32(positions, "positions"); check_i32(cu, "cu_seqlens");
+  TORCH_CHECK(q.dim() == 3 && kpool.dim() == 4 && vpool.dim() == 4 && kpool.is_contiguous() && vpool.is_contiguous() && kpool.scalar_type() == vpool.scalar_type() &&
+              kpool.size(1) == vpool.size(1) && kpool.size(2) == vpool.size(2) && kpool.size(3) == q.size(2),
+              "q fp32 [T, heads, dim]; pools [pages, kv_heads, page, dim] / [pages, kv_heads, page, vdim]");
+  check_act(kpool, "key pool");
+  const int64_t T = q.size(0), H = q.size(1), D = q.size(2), G = kpool.size(1), V = vpool.size(3);
+  TORCH_CHECK(H % G == 0 && V <= 512 && block >= 0 && window >= 0 && positions.numel() >= T, "attention with a sink: vdim <= 512");
+  if (sink.has_value()) { check_f32c(*sink, "sink"); TORCH_CHECK(sink->numel() == H); }
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = out_.has_value() ? *out_ : torch::empty({T, H * V}, kpool.options());
+  check_rows(out, "out");
+  TORCH_CHECK(out.scalar_type() == kpool.scalar_type() && out.size(0) == T && col0 >= 0 && col0 + H * V <= out.size(1));
+  if (T == 0) return out;
+  // the most keys any query of this step can see
+  int64_t span = max_ctx;
+  if (block > 0) span = std::min(span, block);
+  if (window > 0) span = std::min(span, window);
+  // few query rows over long spans (decode): split the keys over CTAs so the grid fills the GPU; a second kernel merges the parts
+  const int nw = b200::sink_attention_warps((int)H, (int)G);
+  const int64_t ctas = T * G * ((H / G + nw - 1) / nw);
+  int64_t nsplit = 1, chunk = 1 << 30;
+  if (ctas < 6 * sm_count() && span > 256) {
+    nsplit = std::min<int64_t>({(6 * sm_count() + ctas - 1) / ctas, (span + 127) / 128, (int64_t)32});
+    chunk = ((span + nsplit - 1) / nsplit + 31) / 32 * 32;
+    nsplit = (span + chunk - 1) / chunk;
+  }
+  Tensor part;
+  if (nsplit > 1) part = torch::empty({T * H * nsplit * (V + 2)}, q.options());
+  else chunk = 1 << 30;
+  LAUNCH_OK(b200::sink_attention_launch(q.data_ptr<float>(), kpool.data_ptr(), vpool.data_ptr(), sink.has_value() ? sink->data_ptr<float>() : nullptr,
+                                        block_tables.data_ptr<int>(), (int)block_tables.size(1), positions.data_ptr<int>(), cu.data_ptr<int>(),
+                                        (int)(cu.numel() - 1), (int)H, (int)G, (int)D, (int)V, (int)kpool.size(2), (int)block, (int)window, (float)scale,
+                                        (float)out_mult, static_cast<char*>(out.data_ptr()) + col0 * out.element_size(), out.stride(0), is_f32(kpool), (int)T,
+                                        (int)nsplit, (int)chunk, nsplit > 1 ? part.data_ptr<float>() : nullptr, cur_stream()));
+  if (nsplit > 1) ++g_launches;
+  return out;
+}
+
+std::vector<Tensor> hy_group_softmax_topk(const Tensor& z, const c10::optional<Tensor>& corr, int64_t E, int64_t top, int64_t ng, int64_t keep) {
+  check_rows(z, "z");
+  TORCH_CHECK(z.is_cuda() && z.scalar_type() == torch::kFloat32 && z.size(1) >= E && top >= 1 && top <= E && ng >= 1 && E % ng == 0 && keep >= 1 && keep <= ng &&
+              top <= keep * (E / ng), "router: top experts out of the kept groups");
+  if (corr.has_value()) { check_f32c(*corr, "correction"); TORCH_CHECK(corr->numel() >= E); }
+  const c10::cuda::CUDAGuard guard(z.device());
+  Tensor idx = torch::empty({z.size(0), top}, z.options().dtype(torch::kInt32)), w = torch::empty({z.size(0), top}, z.options());
+  if (z.size(0) == 0) return {idx, w};
+  LAUNCH_OK(b200::group_softmax_topk_launch(z.data_ptr<float>(), z.stride(0), corr.has_value() ? corr->data_ptr<float>() : nullptr, (int)E, (int)top, (int)ng,
+                                            (int)keep, idx.data_ptr<int>(), w.data_ptr<float>(), (int)z.size(0), cur_stream()));
+  return {idx, w};
+}
+
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mlx_sharding_b200 sm_100a kernels";
   m.def("linear", &linear, py::arg("x"), py::arg("w"), py::arg("w2") = py::none(), py::arg("residual") = py::none(),
@@ -1279,6 +1444,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hy_paged_kv_append", &hy_paged_kv_append);
   m.def("hy_diff_attention", &hy_diff_attention);
   m.def("hy_diff_head_norm", &hy_diff_head_norm);
+  m.def("hy_stream_embed", &hy_stream_embed);
+  m.def("hy_hyper_step_", &hy_hyper_step_);
+  m.def("hy_relu2_", &hy_relu2_);
+  m.def("hy_delta_scan", &hy_delta_scan);
+  m.def("hy_mingru_scan", &hy_mingru_scan, py::arg("rows"), py::arg("z0"), py::arg("x0"), py::arg("g0"), py::arg("width"), py::arg("state"), py::arg("cu"),
+        py::arg("ctx"), py::arg("slots"), py::arg("out_mult"), py::arg("out") = py::none(), py::arg("col0") = 0);
+  m.def("hy_qk_norm_rope_append", &hy_qk_norm_rope_append);
+  m.def("hy_sink_attention", &hy_sink_attention, py::arg("q"), py::arg("kpool"), py::arg("vpool"), py::arg("sink"), py::arg("block_tables"), py::arg("positions"),
+        py::arg("cu"), py::arg("scale"), py::arg("block"), py::arg("window"), py::arg("out_mult"), py::arg("max_ctx"), py::arg("out") = py::none(),
+        py::arg("col0") = 0);
+  m.def("hy_group_softmax_topk", &hy_group_softmax_topk);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

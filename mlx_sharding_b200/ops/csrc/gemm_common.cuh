@@ -160,6 +160,7 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, uint8_t* smem,
         for (int j = 0; j < 16; ++j) {
           float y = g[j] + bias;
           if (DUAL) y = gated_act(p.act, p.act_limit, y, u[j]);
+          else if (p.act == kActRelu2) { y = fmaxf(y, 0.f); y *= y; }
           if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
           stage_store<OutT>(&stg[(c + j) * kTileM + f_local], y);
         }

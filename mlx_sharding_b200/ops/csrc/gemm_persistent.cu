@@ -284,6 +284,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
           for (int j = 0; j < 16; ++j) {
             float y = g[j] + bias;
             if (DUAL) y = gated_act(p.act, p.act_limit, y, u[j]);
+          else if (p.act == kActRelu2) { y = fmaxf(y, 0.f); y *= y; }
             if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
             stage_store<OutT>(&stg[(c - c0 + j) * kTileM + f_local], y);
           }

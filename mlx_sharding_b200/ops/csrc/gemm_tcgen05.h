@@ -8,7 +8,8 @@
 namespace b200 {
 
 // kActClampedGlu (two-weight form only): g' = min(g, act_limit), u' = clamp(u, +-act_limit), y = g' sigmoid(1.702 g') (u' + 1)
-enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2, kActClampedGlu = 3 };
+// kActRelu2: max(y, 0)^2; the only activation that a single-weight product applies (in its epilogue, after bias and split-K reduction)
+enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2, kActClampedGlu = 3, kActRelu2 = 4 };
 
 // Device-side parameter block (passed by value).
 struct GemmParams {
