@@ -53,7 +53,7 @@ def parse_args(argv=None):
     p.add_argument("--fp8-experts", action="store_true",
                    help="convert the routed / shared expert banks to block-scaled MXFP8 at load (tcgen05 kind::mxf8f6f4); this is the "
                         "default for --quant 4/8 checkpoints (MLXB200_FP8_EXPERTS=0 keeps the exact in-kernel MLX-affine dequant)")
-    p.add_argument("--arch", type=str, default=None, choices=["perelorn", "gusolorn", "gifetar"],
+    p.add_argument("--arch", type=str, default=None, choices=["perelorn", "gusolorn", "gifetar", "gokapel"],
                    help="side benchmark (bench/arch_bench.py): that design's prefill / decode throughput and kernel rooflines beside the "
                         "closest existing model; the default workload and its JSON line are not affected")
     p.add_argument("--arch-sizes", type=str, default="1024,2048", help="model widths of --arch")

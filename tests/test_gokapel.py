@@ -61,8 +61,17 @@ DEVICES = [pytest.param("cpu", torch.float32, 2e-4, id="cpu"),
            pytest.param("cuda", torch.bfloat16, 6e-2, id="b200-bf16", marks=pytest.mark.gpu)]
 
 
-def make_cfg(layers, width=48, vocab=96, eps=1e-3, mult=0.5, streams=2, scale=3.0):
-    return dict(architecture="Gokapel", embedding=dict(scale=scale), layers=copy.deepcopy(layers), norm=dict(eps=eps), residual_mult=mult,
+def make_cfg(layers, width=48, vocab=96, eps=1e-3, mult=0.5, streams=2, scale=3.0, dtype=None):
+    """``dtype=bfloat16``: every router takes all experts of all groups.  Under bf16 activations a score moves by a few thousandths, and over
+    hundreds of routing decisions of a stack some choice is always closer than that, so a comparison with exact arithmetic cannot rest on
+    them; the choice itself is compared in exact mode (same kernels, ``float`` instantiation) and, in bf16, on exact inputs (the op tests)."""
+    layers = copy.deepcopy(layers)
+    if dtype == torch.bfloat16:
+        for L in layers:
+            r = (L.get("mlp") or {}).get("router")
+            if r:
+                r["top"], r["groups"]["keep"] = r["experts"], r["groups"]["count"]
+    return dict(architecture="Gokapel", embedding=dict(scale=scale), layers=layers, norm=dict(eps=eps), residual_mult=mult,
                 streams=streams, vocab=vocab, width=width)
 
 
@@ -88,18 +97,6 @@ def toks(n, vocab=96, seed=0):
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-def pick(cfgd, sd, dtype, make, seed, gap=0.02, tries=300):
-    """Tokens ``make(seed)``.  In bf16 a router score moves by a few thousandths, so a test that compares with exact arithmetic must not
-    rest on a choice (of a group or an expert) closer than that: other seeds are tried until the oracle's routing has no close call."""
-    if dtype != torch.bfloat16:
-        return make(seed)
-    for i in range(tries):
-        t = make(seed + 1000 * i)
-        if oracle.min_router_gap(cfgd, sd, t) > gap:
-            return t
-    raise AssertionError("no sequence without a close routing call found")
-
-
 SHOWS = 1e-2      # a fault must move the logits by this share of their largest: 50 times the exact-mode tolerance
 
 
@@ -121,9 +118,9 @@ def decode_after(model, t, n_prompt, **kw):
 def test_mechanism_against_oracle(case, device, dtype, tol):
     """Each layer shape alone (and the mixed stack with two layers that run on another layer's weights): whole prompt, every position;
     45 tokens span three 16-token pages and several blocks."""
-    cfgd = make_cfg(CASES[case], streams=3 if case == "par_mq" else 2)
+    cfgd = make_cfg(CASES[case], streams=3 if case == "par_mq" else 2, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
-    t = pick(cfgd, sd, dtype, lambda s: toks(45, seed=s), 0)
+    t = toks(45, seed=0)
     lo = []
     want = oracle.forward(cfgd, sd, t, layers_out=lo)
     got_layers = []
@@ -251,9 +248,9 @@ def test_attention_alone(device, dtype, tol):
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES)
 def test_first_tokens_and_single_token(device, dtype, tol):
-    cfgd = make_cfg(STACK)
+    cfgd = make_cfg(STACK, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
-    for t in ([5], pick(cfgd, sd, dtype, lambda s: toks(2, seed=s), 4), pick(cfgd, sd, dtype, lambda s: toks(3, seed=s), 5)):
+    for t in ([5], toks(2, seed=4), toks(3, seed=5)):
         close(run_whole(model, t), oracle.forward(cfgd, sd, t), tol)
 
 
@@ -262,9 +259,9 @@ def test_first_tokens_and_single_token(device, dtype, tol):
 def test_portions_equal_whole(portions, device, dtype, tol):
     """Prefill against token-by-token decoding and prompts cut anywhere (page edge at 16, block edges at 7, 14, 16, 21, convolution
     histories of 1 and 3 inputs that start inside the previous portion, 2-token portions)."""
-    cfgd = make_cfg(STACK)
+    cfgd = make_cfg(STACK, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
-    t = pick(cfgd, sd, dtype, lambda s: toks(sum(portions), seed=s), 1)
+    t = toks(sum(portions), seed=1)
     want = oracle.forward(cfgd, sd, t)
     s, at, got = session(model), 0, []
     for n in portions:
@@ -277,9 +274,9 @@ def test_portions_equal_whole(portions, device, dtype, tol):
 def test_ragged_batch_and_reuse_of_pages_and_slots(device, dtype, tol):
     """Unequal requests in one batch (portions beside single tokens) equal each alone; a pool of 5 pages and 2 state slots serves 4
     requests one pair after another, so every page and slot is used again — by a request that must not see what the last one left."""
-    cfgd = make_cfg(STACK)
+    cfgd = make_cfg(STACK, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
-    reqs = {n: pick(cfgd, sd, dtype, lambda s, L=L: toks(L, seed=s), 10 + i) for i, (n, L) in enumerate([("a", 30), ("b", 9), ("c", 17), ("d", 33)])}
+    reqs = {n: toks(L, seed=10 + i) for i, (n, L) in enumerate([("a", 30), ("b", 9), ("c", 17), ("d", 33)])}
     want = {n: oracle.forward(cfgd, sd, t) for n, t in reqs.items()}
     s = session(model, pages=6, page_size=16, live=2)
     assert s.table.slots is not None and s.table.slots.num_free == 2
@@ -311,7 +308,7 @@ def test_block_edges_show(device, dtype, tol):
     make single keys count; the oracle with blocks of 8 or 10 gives other logits at positions around the edges, so a limit that is one
     off would show.  In a prompt, in portions that start inside a block, and decoded one by one across edges and a page border."""
     layer = par(4, 2, 8, 12, 9, 4, 0.6, 10, None, ls=1.0, rs=0.1)
-    cfgd = make_cfg([layer])
+    cfgd = make_cfg([layer], dtype=dtype)
     model, sd = make_model(cfgd, device, dtype, edit=lambda sd: sd["l0.mix.left.q"].mul_(4.0))
     t = toks(40, seed=7)
     want = oracle.forward(cfgd, sd, t)
@@ -334,7 +331,7 @@ def test_block_edges_show(device, dtype, tol):
 def test_sink_shows(device, dtype, tol):
     """Large sinks take most of the softmax mass at short contexts: leaving them out, or scaling them like a score, moves the logits."""
     layer = par(4, 2, 8, 12, 12, 8, 0.3, 10, None, ls=1.0, rs=0.1)
-    cfgd = make_cfg([layer], mult=1.0)
+    cfgd = make_cfg([layer], mult=1.0, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype, edit=lambda sd: sd["l0.mix.left.sink"].copy_(torch.tensor([3.0, 1.0, 2.0, 4.0])))
     t = toks(30, seed=8)
     want = oracle.forward(cfgd, sd, t)
@@ -351,10 +348,10 @@ def test_far_token_lives_in_the_state(kind, device, dtype, tol):
     the first eight tokens to position 60 and beyond, four pages on: other tokens there move the late logits; a state that was lost or
     not carried across steps would show.  In a prompt, in decoding, and in portions."""
     if kind == "delta":
-        cfgd = make_cfg([delta(2, 1, 8, 12, 2, None)], mult=1.0)
+        cfgd = make_cfg([delta(2, 1, 8, 12, 2, None)], mult=1.0, dtype=dtype)
         edit = lambda sd: (sd["l0.mix.A_log"].fill_(-6.0), sd["l0.mix.dt_bias"].fill_(-3.0), sd["l0.mix.o"].mul_(3.0))
     else:
-        cfgd = make_cfg([par(2, 1, 8, 12, 8, 4, 0.3, 24, None, ls=0.2, rs=1.5)], mult=1.0)
+        cfgd = make_cfg([par(2, 1, 8, 12, 8, 4, 0.3, 24, None, ls=0.2, rs=1.5)], mult=1.0, dtype=dtype)
         edit = lambda sd: (sd["l0.mix.right.z.b"].fill_(-4.5), sd["l0.mix.right.z"].mul_(0.3), sd["l0.mix.right.o"].mul_(6.0))
     model, sd = make_model(cfgd, device, dtype, edit=edit)
     for seed in range(40):
@@ -378,7 +375,7 @@ def test_far_token_lives_in_the_state(kind, device, dtype, tol):
 def test_long_prompt_then_decode(device, dtype, tol):
     """A 290-token prompt over blocks of 300 positions (one block) and without a block limit, then single tokens whose keys are split
     over CTAs and merged (with the sink in the merge) on the GPU."""
-    cfgd = make_cfg([par(4, 2, 8, 12, 300, 8, 0.3, 16, MOE_ALL), par(2, 1, 16, 40, 0, 4, 0.2, 8, None), delta(2, 2, 8, 8, 3, None)])
+    cfgd = make_cfg([par(4, 2, 8, 12, 300, 8, 0.3, 16, MOE_ALL), par(2, 1, 16, 40, 0, 4, 0.2, 8, None), delta(2, 2, 8, 8, 3, None)], dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
     t = toks(296, seed=9)
     want = oracle.forward(cfgd, sd, t)
@@ -391,9 +388,9 @@ def test_long_prompt_then_decode(device, dtype, tol):
 @pytest.mark.parametrize("device,dtype,tol", DEVICES)
 def test_long_decode(device, dtype, tol):
     """150 single-token steps after a 3-token prompt: states are read and written every step, blocks and pages come and go."""
-    cfgd = make_cfg([D_GQ, P_GQ, D_ONE])
+    cfgd = make_cfg([D_GQ, P_GQ, D_ONE], dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
-    t = pick(cfgd, sd, dtype, lambda s: toks(153 if dtype != torch.bfloat16 else 60, seed=s), 5, gap=0.01, tries=400)
+    t = toks(153 if dtype != torch.bfloat16 else 60, seed=5)
     close(decode_after(model, t, 3), oracle.forward(cfgd, sd, t), tol * (3 if dtype == torch.bfloat16 else 1))
 
 
@@ -403,9 +400,9 @@ def test_tensor_core_sizes(dtype, tol):
     """Width, feed-forward and expert rows that are multiples of 128, head sizes that are multiples of 8: bf16 takes the tensor-core GEMMs
     (squared ReLU in the epilogue of the dense and the grouped product); value widths of 128 use several registers per lane."""
     moe = dict(kind="moe", router=dict(experts=8, top=2, groups=dict(count=4, keep=2)), expert=dict(ff=128), shared=dict(ff=128))
-    cfgd = make_cfg([delta(4, 2, 16, 32, 4, moe), par(4, 2, 16, 128, 24, 8, 0.25, 64, dict(kind="dense", ff=256)), delta(2, 2, 64, 64, 4, None)], width=128)
+    cfgd = make_cfg([delta(4, 2, 16, 32, 4, moe), par(4, 2, 16, 128, 24, 8, 0.25, 64, dict(kind="dense", ff=256)), delta(2, 2, 64, 64, 4, None)], width=128, dtype=dtype)
     model, sd = make_model(cfgd, "cuda", dtype)
-    t = pick(cfgd, sd, dtype, lambda s: toks(44, seed=s), 2, gap=0.01, tries=400)
+    t = toks(44, seed=2)
     close(decode_after(model, t, 40), oracle.forward(cfgd, sd, t), tol)
 
 
@@ -413,7 +410,7 @@ def test_tensor_core_sizes(dtype, tol):
 def test_greedy_generation_through_engine(device, dtype, tol):
     """The engine's scheduler, sampler and (on the GPU) captured decode graphs: two requests of unequal length, greedy tokens equal
     the oracle's argmax continuation; pages and slots come back."""
-    cfgd = make_cfg(STACK)
+    cfgd = make_cfg(STACK, dtype=dtype)
     model, sd = make_model(cfgd, device, dtype)
     eng = LLMEngine(LocalPipeline([StageExecutor(model, 16, 16, num_state_slots=4)]), 16, 16, num_groups=1, max_prefill_tokens=11)
     assert eng.table.slots is not None
