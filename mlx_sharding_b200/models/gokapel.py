@@ -44,6 +44,7 @@ from .perelorn import _pad_rows
 
 class GokapelStage(StageModel):
     arch = "gokapel"
+    PREFILL_GEMM_MIN_ROWS = 32
     UNIT_EPS = 1e-6            # inside the root of the unit vectors of the delta rule (fixed by the design)
 
     def __init__(self, cfg, spec=None, dtype=torch.bfloat16, device="cpu", backend=None):
@@ -224,7 +225,8 @@ class GokapelStage(StageModel):
         q = O.qk_norm_rope_append(u, seg["q"][0], seg["k"][0], seg["v"][0], H, D, w["qn"], w["kn"], eps, w["inv_freq"], kpool, vpool, meta)
         both = torch.zeros(T, w["o_split"] + R, dtype=self.dtype, device=u.device) if w["o_split"] != H * V else \
             torch.empty(T, H * V + R, dtype=self.dtype, device=u.device)
-        O.sink_attention(q, kpool, vpool, w["sink"], meta, float(a["scale"]), int((a.get("mask") or {}).get("size", 0) or 0), 0,
+        attend = O.sink_attention_prefill if (meta.num_seqs == 1 and T >= self.PREFILL_GEMM_MIN_ROWS) else O.sink_attention
+        attend(q, kpool, vpool, w["sink"], meta, float(a["scale"]), int((a.get("mask") or {}).get("size", 0) or 0), 0,
                          float(m.get("left_scale", 1.0)), self.dtype, both, 0)
         O.mingru_scan(u, seg["z"][0], seg["x"][0], seg["g"][0], R, st["S"], meta, float(m.get("right_scale", 1.0)), self.dtype, both, w["o_split"])
         return self._mm(both, w["o"], True), (self._cols(u, seg, "rg") if "rg" in seg else None)

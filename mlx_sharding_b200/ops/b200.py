@@ -819,10 +819,61 @@ def sink_attention(q, kpool, vpool, sink, meta: BatchMeta, scale: float, block: 
                                  float(out_mult), int(meta.max_ctx_len), out, int(out_col0))
 
 
+SINK_PREFILL_MIN_BLOCK = 256     # blocks of fewer positions: the products are too small to pay for their launches; the ragged kernel runs
+
+
+def sink_attention_prefill(q, kpool, vpool, sink, meta: BatchMeta, scale: float, block: int = 0, window: int = 0, out_mult: float = 1.0, out_dtype=None,
+                           out=None, out_col0: int = 0):
+    """:func:`sink_attention` for a step that holds ONE sequence with many query rows (a prompt or a portion of one), as matrix products per
+    block of positions and key / value head ``g``: gather the sequence's cached keys ``K_g`` and values ``V_g`` from the first visible
+    position on, then for every block that holds queries of this step ``S = Q K_g[block]^T`` (fp32 out) for the ``H / G`` query heads of the
+    group at once, the causal softmax with the sink (``hy_sink_softmax``; all keys of the slice lie in the queries' own block, so no lower
+    limit is needed), ``O = P V_g[block]``.  The products run on the tensor cores (tcgen05 GEMM; cuBLAS fp32 in exact mode); query rows go in
+    pieces so that a score matrix stays below 256 MB.  Sliding windows, blocks that are small or not a multiple of 8 positions: the kernel."""
+    T, H, D = q.shape
+    P, G, page, _ = kpool.shape
+    V, Rg, adt = vpool.shape[3], H // G, kpool.dtype
+    if window > 0 or meta.num_seqs != 1 or (block > 0 and (block % 8 != 0 or block < SINK_PREFILL_MIN_BLOCK)):
+        return sink_attention(q, kpool, vpool, sink, meta, scale, block, window, out_mult, out_dtype, out, out_col0)
+    ctx = int(meta.max_ctx_len)
+    ctx0 = ctx - T
+    first = ctx0 // block * block if block > 0 else 0                # first position any query of this step sees
+    nk = ctx - first
+    npad = (nk + 7) // 8 * 8
+    pages = meta.block_tables[0, first // page:(ctx + page - 1) // page].long()
+    skip = first - first // page * page
+    # [G, keys from `first` on (padded with any finite rows: they lie behind every query), .] copies of this sequence's keys and values
+    Kc = kpool[pages].permute(1, 0, 2, 3).reshape(G, -1, D)[:, skip:]
+    Vc = vpool[pages].permute(1, 0, 2, 3).reshape(G, -1, V)[:, skip:]
+    if Kc.shape[1] < npad:
+        Kc, Vc = torch.nn.functional.pad(Kc, (0, 0, 0, npad - Kc.shape[1])), torch.nn.functional.pad(Vc, (0, 0, 0, npad - Vc.shape[1]))
+    Kc, Vt = Kc[:, :npad].contiguous(), Vc[:, :npad].transpose(1, 2).contiguous()                  # [G, npad, D], [G, V, npad]
+    if out is None:
+        out, out_col0 = torch.empty(T, H * V, dtype=adt, device=q.device), 0
+    qa = q.to(adt).view(T, G, Rg, D)
+    is32 = _is32(adt)
+    span = block if block > 0 else ctx
+    piece = max(1, (1 << 26) // (min(npad, span + 8) * Rg))
+    for bs in range(first, ctx, span):
+        be = min(bs + span, ctx)
+        t_lo, t_hi = max(bs, ctx0) - ctx0, be - ctx0
+        for t0 in range(t_lo, t_hi, piece):
+            n = min(t_hi, t0 + piece) - t0
+            ka, kb = bs - first, min(npad, (ctx0 + t0 + n - first + 7) // 8 * 8)            # keys this piece can see, as rows of Kc
+            for g in range(G):
+                sg = None if sink is None else sink[g * Rg:(g + 1) * Rg]
+                sc = linear_any(qa[t0:t0 + n, g].reshape(n * Rg, D), LinearWeight(weight=Kc[g, ka:kb]), torch.float32)
+                pr = C().hy_sink_softmax(sc, sg, int(Rg), int(ctx0 + t0), float(scale), is32, 0, int(bs), 0.0, 0.0, 1.0)
+                o = linear_any(pr, LinearWeight(weight=Vt[g, :, ka:kb].contiguous()), torch.float32)
+                c0 = out_col0 + g * Rg * V
+                out[t0:t0 + n, c0:c0 + Rg * V] = (o * out_mult).view(n, Rg * V)
+    return out
+
+
 def mingru_scan(rows, z_col0: int, x_col0: int, g_col0: int, width: int, state, meta: BatchMeta, out_mult: float = 1.0, out_dtype=None, out=None,
                 out_col0: int = 0):
     return C().hy_mingru_scan(rows, int(z_col0), int(x_col0), int(g_col0), int(width), state, meta.cu_seqlens, meta.context_lens, _slots(meta),
-                              float(out_mult), out, int(out_col0))
+                              float(out_mult), int(meta.max_q_len), out, int(out_col0))
 
 
 def group_softmax_topk(z, correction, num_experts: int, top: int, n_groups: int = 1, keep_groups: int = 1):

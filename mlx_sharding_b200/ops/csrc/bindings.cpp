@@ -1253,7 +1253,7 @@ Tensor hy_delta_scan(const Tensor& qkv, const Tensor& beta, const Tensor& dt, co
 
 // out (optional): AT [T, >= col0 + width], the result goes to its columns col0 .. col0 + width
 Tensor hy_mingru_scan(const Tensor& rows, int64_t z0, int64_t x0, int64_t g0, int64_t R, Tensor state, const Tensor& cu, const Tensor& ctx, const Tensor& slots,
-                      double out_mult, const c10::optional<Tensor>& out_, int64_t col0) {
+                      double out_mult, int64_t max_q, const c10::optional<Tensor>& out_, int64_t col0) {
   check_act(rows, "rows"); check_rows(rows, "rows"); check_f32c(state, "state"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens");
   check_i32(slots, "state_slots");
   TORCH_CHECK(R >= 1 && z0 >= 0 && x0 >= 0 && g0 >= 0 && std::max({z0, x0, g0}) + R <= rows.size(1) && state.dim() == 2 && state.size(1) == R);
@@ -1264,7 +1264,7 @@ Tensor hy_mingru_scan(const Tensor& rows, int64_t z0, int64_t x0, int64_t g0, in
   if (rows.size(0) == 0) return out;
   LAUNCH_OK(b200::mingru_scan_launch(rows.data_ptr(), rows.stride(0), (int)z0, (int)x0, (int)g0, (int)R, state.data_ptr<float>(), cu.data_ptr<int>(),
                                      ctx.data_ptr<int>(), slots.data_ptr<int>(), (float)out_mult,
-                                     static_cast<char*>(out.data_ptr()) + col0 * out.element_size(), out.stride(0), (int)slots.numel(), is_f32(rows), cur_stream()));
+                                     static_cast<char*>(out.data_ptr()) + col0 * out.element_size(), out.stride(0), (int)slots.numel(), is_f32(rows), (int)max_q, cur_stream()));
   return out;
 }
 
@@ -1449,7 +1449,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hy_relu2_", &hy_relu2_);
   m.def("hy_delta_scan", &hy_delta_scan);
   m.def("hy_mingru_scan", &hy_mingru_scan, py::arg("rows"), py::arg("z0"), py::arg("x0"), py::arg("g0"), py::arg("width"), py::arg("state"), py::arg("cu"),
-        py::arg("ctx"), py::arg("slots"), py::arg("out_mult"), py::arg("out") = py::none(), py::arg("col0") = 0);
+        py::arg("ctx"), py::arg("slots"), py::arg("out_mult"), py::arg("max_q"), py::arg("out") = py::none(), py::arg("col0") = 0);
   m.def("hy_qk_norm_rope_append", &hy_qk_norm_rope_append);
   m.def("hy_sink_attention", &hy_sink_attention, py::arg("q"), py::arg("kpool"), py::arg("vpool"), py::arg("sink"), py::arg("block_tables"), py::arg("positions"),
         py::arg("cu"), py::arg("scale"), py::arg("block"), py::arg("window"), py::arg("out_mult"), py::arg("max_ctx"), py::arg("out") = py::none(),

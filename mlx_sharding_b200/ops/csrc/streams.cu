@@ -186,29 +186,45 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
 }
 
 // ---------------------------------------------------------------------------------------------------------- minGRU
-// One thread per (sequence, channel): z = sigmoid(rows[z]), c = u + 1/2 (u >= 0) or sigmoid(u), S <- (1 - z) S + z c,
-// out = S * silu(rows[g]) * out_mult.                                                      grid (B, ceil(R / blockDim))
+// z = sigmoid(rows[z]), c = u + 1/2 (u >= 0) or sigmoid(u), S <- (1 - z) S + z c, out = S * silu(rows[g]) * out_mult.
+// The recurrence is linear in S, so a sequence's tokens are cut into TS slices: thread (channel, slice) first folds its slice into
+// (A, B) with S_end = A S_start + B, then takes its start from the slices before it (at most TS - 1 steps) and runs its slice again,
+// writing the outputs.  Decode (one token) is the TS = 1 case.                     grid (B, ceil(R / 32)), block (32 channels, TS)
 template <typename AT>
 __global__ void mingru_scan_kernel(const AT* __restrict__ rows, long long ld, int z0, int x0, int g0, int R, float* __restrict__ state,
                                    const int* __restrict__ cu, const int* __restrict__ ctx, const int* __restrict__ slots, float out_mult,
                                    AT* __restrict__ out, long long ld_out) {
-  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= R) return;
+  __shared__ float fa[32][33], fb[32][33];
+  const int b = blockIdx.x, cl = threadIdx.x, sl = threadIdx.y, TS = blockDim.y, c = blockIdx.y * 32 + cl;
   const int s = cu[b], q = cu[b + 1] - s;
   if (q == 0) return;
+  const int len = (q + TS - 1) / TS, j0 = min(q, sl * len), j1 = min(q, j0 + len);
+  const bool live = c < R;
+  const AT* row = rows + (long long)(s + j0) * ld + c;
+  float A = 1.f, Bv = 0.f;
+  if (live && TS > 1) {
+    const AT* r = row;
+    for (int j = j0; j < j1; ++j, r += ld) {
+      const float z = sigmoid_f(ldf<AT>(r + z0)), u = ldf<AT>(r + x0);
+      const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+      A *= 1.f - z;
+      Bv = (1.f - z) * Bv + z * cand;
+    }
+  }
+  fa[sl][cl] = A; fb[sl][cl] = Bv;
+  __syncthreads();
+  if (!live) return;
   float* st = state + (long long)slots[b] * R + c;
   float S = ctx[b] - q == 0 ? 0.f : *st;
-  const AT* row = rows + (long long)s * ld + c;
-  AT* orow = out + (long long)s * ld_out + c;
-#pragma unroll 4
-  for (int j = 0; j < q; ++j) {
-    const float zr = ldf<AT>(row + z0), u = ldf<AT>(row + x0), gr = ldf<AT>(row + g0);
-    const float z = sigmoid_f(zr), cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+  for (int i = 0; i < sl; ++i) S = fa[i][cl] * S + fb[i][cl];
+  AT* orow = out + (long long)(s + j0) * ld_out + c;
+  for (int j = j0; j < j1; ++j, row += ld, orow += ld_out) {
+    const float z = sigmoid_f(ldf<AT>(row + z0)), u = ldf<AT>(row + x0), gr = ldf<AT>(row + g0);
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
     S = (1.f - z) * S + z * cand;
     stf<AT>(orow, S * silu_f(gr) * out_mult);
-    row += ld; orow += ld_out;
   }
-  *st = S;
+  if (sl == TS - 1) *st = S;          // the last slice ends at the sequence's last token (empty slices pass S through)
 }
 
 // ---------------------------------------------------------------------------------------------------------- attention prologue
@@ -505,9 +521,11 @@ cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta,
 }
 
 cudaError_t mingru_scan_launch(const void* rows, long long ld, int z0, int x0, int g0, int R, float* state, const int* cu, const int* ctx,
-                               const int* slots, float out_mult, void* out, long long ld_out, int B, bool f32, cudaStream_t s) {
-  dim3 grid(B, (R + 127) / 128);
-  AT_DISPATCH(f32, (mingru_scan_kernel<AT><<<grid, 128, 0, s>>>((const AT*)rows, ld, z0, x0, g0, R, state, cu, ctx, slots, out_mult, (AT*)out, ld_out)));
+                               const int* slots, float out_mult, void* out, long long ld_out, int B, bool f32, int max_q, cudaStream_t s) {
+  int TS = 1;                                   // slices of at least 16 tokens, at most 32 of them
+  while (TS < 32 && max_q >= 32 * TS) TS *= 2;
+  dim3 grid(B, (R + 31) / 32), block(32, TS);
+  AT_DISPATCH(f32, (mingru_scan_kernel<AT><<<grid, block, 0, s>>>((const AT*)rows, ld, z0, x0, g0, R, state, cu, ctx, slots, out_mult, (AT*)out, ld_out)));
   return last();
 }
 

@@ -16,7 +16,7 @@ cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta,
                               const float* dt_bias, const float* A_log, float* state, const int* cu, const int* ctx, const int* slots, float* out,
                               int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, cudaStream_t s);
 cudaError_t mingru_scan_launch(const void* rows, long long ld, int z0, int x0, int g0, int R, float* state, const int* cu, const int* ctx,
-                               const int* slots, float out_mult, void* out, long long ld_out, int B, bool f32, cudaStream_t s);
+                               const int* slots, float out_mult, void* out, long long ld_out, int B, bool f32, int max_q, cudaStream_t s);
 cudaError_t qk_norm_rope_append_launch(const void* rows, long long ld, int q0, int k0, int v0, int H, int G, int D, int V, const float* qn,
                                        const float* kn, float eps, const float* inv_freq, int rot, const int* positions, const int* slot_map,
                                        int page, float* qout, void* kpool, void* vpool, bool f32, int T, cudaStream_t s);

@@ -853,6 +853,12 @@ def sink_attention(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, si
     return out
 
 
+def sink_attention_prefill(q, kpool, vpool, sink, meta: BatchMeta, scale: float, block: int = 0, window: int = 0, out_mult: float = 1.0,
+                           out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None, out_col0: int = 0) -> torch.Tensor:
+    """Single-sequence prefill form of :func:`sink_attention` (the CUDA backend runs it as matrix products); same math here."""
+    return sink_attention(q, kpool, vpool, sink, meta, scale, block, window, out_mult, out_dtype, out, out_col0)
+
+
 def mingru_scan(rows: torch.Tensor, z_col0: int, x_col0: int, g_col0: int, width: int, state: torch.Tensor, meta: BatchMeta,
                 out_mult: float = 1.0, out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None, out_col0: int = 0) -> torch.Tensor:
     """Element-wise gated recurrence whose gates read the current token only (fp32): ``z = sigmoid(rows[z])``, candidate ``c = u + 1/2``

@@ -386,6 +386,24 @@ def test_long_prompt_then_decode(device, dtype, tol):
 
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES)
+def test_long_portions_across_blocks(device, dtype, tol):
+    """Portions of 40, 250 and 44 tokens over blocks of 256 positions and without a block limit: the second portion starts inside the first
+    block and ends in the second (on the GPU long portions of one sequence take the matrix-product form of the attention, block by block,
+    and the minGRU runs its slices of the portion side by side)."""
+    cfgd = make_cfg([par(4, 2, 8, 12, 256, 8, 0.3, 40, None), par(2, 1, 16, 40, 0, 4, 0.2, 8, DENSE)], dtype=dtype)
+    model, sd = make_model(cfgd, device, dtype)
+    t = toks(334, seed=19)
+    want = oracle.forward(cfgd, sd, t)
+    s, at, got, rows = session(model, pages=23), 0, [], []
+    for n in (40, 250, 44):
+        want_rows = sorted({0, 1, n // 2, n - 2, n - 1} | {r - at for r in (255, 256, 257) if at <= r < at + n})
+        got.append(s.step([dict(id="r", tokens=t[at:at + n], want=want_rows)]))
+        rows += [at + r for r in want_rows]
+        at += n
+    close(torch.cat(got), want[rows], tol * (3 if dtype == torch.bfloat16 else 1))
+
+
+@pytest.mark.parametrize("device,dtype,tol", DEVICES)
 def test_long_decode(device, dtype, tol):
     """150 single-token steps after a 3-token prompt: states are read and written every step, blocks and pages come and go."""
     cfgd = make_cfg([D_GQ, P_GQ, D_ONE], dtype=dtype)
