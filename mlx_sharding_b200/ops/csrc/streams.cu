@@ -111,9 +111,10 @@ constexpr int kDeltaTokensMax = 16;
 //   S <- g S, partial S^T k  |  u = beta (v - S^T k), S <- S + k u^T, partial S^T q  |  o
 template <typename AT>
 __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, p0 = blockIdx.z * PB;
   const int g = h / (H / a.G);
+  const bool vec4 = PB % 4 == 0 && P % 4 == 0;          // 16-byte copies of the state block (rows of PB floats at a stride of P)
   const int p = threadIdx.x % PB, r = threadIdx.x / PB, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   float* S = smem;                          // [N][PB]
   float* red1 = S + N * PB;                 // [R][PB]
@@ -125,7 +126,14 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
   if (q == 0) return;
   const bool fresh = a.ctx[b] - q == 0;
   float* gS = a.state + ((long long)a.slots[b] * H + h) * N * P;
-  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; S[e] = fresh ? 0.f : gS[n * P + p0 + c]; }
+  if (vec4) {
+    for (int e = 4 * threadIdx.x; e < N * PB; e += 4 * blockDim.x) {
+      const int n = e / PB, c = e % PB;
+      *reinterpret_cast<float4*>(S + e) = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(gS + n * P + p0 + c);
+    }
+  } else {
+    for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; S[e] = fresh ? 0.f : gS[n * P + p0 + c]; }
+  }
   const AT* in = reinterpret_cast<const AT*>(a.in);
   const float negA = -expf(a.A_log[h]);
   const int GN = a.G * N;
@@ -182,7 +190,14 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = S[e]; }
+  if (vec4) {
+    for (int e = 4 * threadIdx.x; e < N * PB; e += 4 * blockDim.x) {
+      const int n = e / PB, c = e % PB;
+      *reinterpret_cast<float4*>(gS + n * P + p0 + c) = *reinterpret_cast<const float4*>(S + e);
+    }
+  } else {
+    for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = S[e]; }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------- minGRU
@@ -204,6 +219,7 @@ __global__ void mingru_scan_kernel(const AT* __restrict__ rows, long long ld, in
   float A = 1.f, Bv = 0.f;
   if (live && TS > 1) {
     const AT* r = row;
+#pragma unroll 4
     for (int j = j0; j < j1; ++j, r += ld) {
       const float z = sigmoid_f(ldf<AT>(r + z0)), u = ldf<AT>(r + x0);
       const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
@@ -218,6 +234,7 @@ __global__ void mingru_scan_kernel(const AT* __restrict__ rows, long long ld, in
   float S = ctx[b] - q == 0 ? 0.f : *st;
   for (int i = 0; i < sl; ++i) S = fa[i][cl] * S + fb[i][cl];
   AT* orow = out + (long long)(s + j0) * ld_out + c;
+#pragma unroll 4
   for (int j = j0; j < j1; ++j, row += ld, orow += ld_out) {
     const float z = sigmoid_f(ldf<AT>(row + z0)), u = ldf<AT>(row + x0), gr = ldf<AT>(row + g0);
     const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
@@ -288,14 +305,21 @@ __device__ __forceinline__ int first_key(int pos, int block, int window) {
   return lo;
 }
 
+// value column of register i of a lane: VEC (vdim a multiple of 128) 4 lane + 128 (i / 4) + i % 4 — four adjacent columns per 16-byte
+// shared-memory load —, else lane + 32 i
+template <bool VEC>
+__device__ __forceinline__ int sink_vcol(int lane, int i) { return VEC ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i; }
+
 // grid (tokens, G * ceil((H/G) / warps), key splits); one warp per query head, the warps of a CTA share one key / value head whose tile
 // of kTile keys and values is staged in shared memory as floats.  Lane j scores key j of the tile; the running softmax (m, l) and the
-// accumulator live in registers, lane owning value columns lane + 32 i.  Key splits count from the first visible key.
-template <typename AT, int NPL>
+// accumulator live in registers, lane owning the value columns sink_vcol(lane, i).  Key splits count from the first visible key.
+// VEC (dim a multiple of the 16-byte chunk, vdim a multiple of 128): 16-byte shared-memory stores and loads in all phases, key rows
+// padded by 4 floats; else scalar accesses, key rows padded by 1.
+template <typename AT, int NPL, bool VEC>
 __global__ void sink_attention_kernel(SinkAttnArgs a) {
   extern __shared__ __align__(16) float smem[];
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int D = a.D, V = a.V, ldk = D + 1;
+  const int D = a.D, V = a.V, ldk = VEC ? D + 4 : D + 1;
   float* qs = smem;                         // [nw][D]
   float* ks = qs + nw * D;                  // [tile][D + 1]
   float* vs = ks + kTile * ldk;             // [tile][V]
@@ -327,7 +351,15 @@ __global__ void sink_attention_kernel(SinkAttnArgs a) {
       const AT* vsrc = (const AT*)a.vpool + base * V;
       float* kd = ks + jj * ldk;
       float* vd = vs + jj * V;
-      if (vec) {
+      if (VEC) {
+        for (int c = lane; c < (D + V) / E; c += 32) {
+          float f[E];
+          unpack16<AT>(*reinterpret_cast<const uint4*>(c < D / E ? ksrc + c * E : vsrc + (c - D / E) * E), f);
+          float* dst = c < D / E ? kd + c * E : vd + (c - D / E) * E;
+#pragma unroll
+          for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+        }
+      } else if (vec) {
         for (int c = lane; c < D / E; c += 32) { float f[E]; unpack16<AT>(*reinterpret_cast<const uint4*>(ksrc + c * E), f);
 #pragma unroll
           for (int e = 0; e < E; ++e) kd[c * E + e] = f[e]; }
@@ -343,7 +375,13 @@ __global__ void sink_attention_kernel(SinkAttnArgs a) {
     if (lane < nk) {
       const float* kr = ks + lane * ldk;
       float d = 0.f;
-      for (int i = 0; i < D; ++i) d += qh[i] * kr[i];
+      if (VEC) {
+        const float4* q4 = reinterpret_cast<const float4*>(qh);
+        const float4* k4 = reinterpret_cast<const float4*>(kr);
+        for (int i = 0; i < (D >> 2); ++i) { const float4 x = q4[i], y = k4[i]; d += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w; }
+      } else {
+        for (int i = 0; i < D; ++i) d += qh[i] * kr[i];
+      }
       sc = d;
     }
     const float nm = fmaxf(m, warp_max(sc));
@@ -356,10 +394,19 @@ __global__ void sink_attention_kernel(SinkAttnArgs a) {
     for (int jj = 0; jj < nk; ++jj) {
       const float w = __shfl_sync(0xffffffffu, pw, jj);
       const float* vr = vs + jj * V;
+      if (VEC) {
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < V) o[i] += w * vr[d];
+        for (int i = 0; i < NPL / 4; ++i)
+          if (128 * i < V) {
+            const float4 c = *reinterpret_cast<const float4*>(vr + 4 * lane + 128 * i);
+            o[4 * i] += w * c.x; o[4 * i + 1] += w * c.y; o[4 * i + 2] += w * c.z; o[4 * i + 3] += w * c.w;
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          const int d = lane + 32 * i;
+          if (d < V) o[i] += w * vr[d];
+        }
       }
     }
   }
@@ -370,12 +417,12 @@ __global__ void sink_attention_kernel(SinkAttnArgs a) {
     const float inv = a.out_mult / l;
     AT* orow = (AT*)a.out + (long long)t * a.ld_out + (long long)h * V;
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) { const int d = lane + 32 * i; if (d < V) stf<AT>(orow + d, o[i] * inv); }
+    for (int i = 0; i < NPL; ++i) { const int d = sink_vcol<VEC>(lane, i); if (d < V) stf<AT>(orow + d, o[i] * inv); }
   } else {
     float* pp = a.part + (((long long)t * a.H + h) * a.nsplit + blockIdx.z) * (V + 2);
     if (lane == 0) { pp[0] = m; pp[1] = l; }
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) { const int d = lane + 32 * i; if (d < V) pp[2 + d] = o[i]; }
+    for (int i = 0; i < NPL; ++i) { const int d = sink_vcol<VEC>(lane, i); if (d < V) pp[2 + d] = o[i]; }
   }
 }
 
@@ -544,11 +591,11 @@ int sink_attention_warps(int H, int G) {
   return rg < 8 ? rg : 8;
 }
 
-template <typename AT, int NPL>
+template <typename AT, int NPL, bool VEC>
 static cudaError_t sink_attention_t(const SinkAttnArgs& a, int T, cudaStream_t s) {
   const int nw = sink_attention_warps(a.H, a.G), nb = (a.H / a.G + nw - 1) / nw;
-  const size_t smem = ((size_t)nw * a.D + (size_t)kTile * (a.D + 1) + (size_t)kTile * a.V) * sizeof(float);
-  auto k = sink_attention_kernel<AT, NPL>;
+  const size_t smem = ((size_t)nw * a.D + (size_t)kTile * (a.D + (VEC ? 4 : 1)) + (size_t)kTile * a.V) * sizeof(float);
+  auto k = sink_attention_kernel<AT, NPL, VEC>;
   if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
   k<<<dim3(T, a.G * nb, a.nsplit), 32 * nw, smem, s>>>(a);
   if (a.nsplit > 1) sink_combine_kernel<AT, NPL><<<T * a.H, 32, 0, s>>>(a.part, a.sink, a.H, a.V, a.nsplit, a.out_mult, (AT*)a.out, a.ld_out);
@@ -559,11 +606,18 @@ cudaError_t sink_attention_launch(const float* q, const void* kpool, const void*
                                   const int* positions, const int* cu, int B, int H, int G, int D, int V, int page, int block, int window,
                                   float scale, float out_mult, void* out, long long ld_out, bool f32, int T, int nsplit, int chunk, float* part,
                                   cudaStream_t s) {
-  if (G < 1 || H % G != 0 || V > 512 || (size_t)(8 * D + kTile * (D + 1) + kTile * V) * sizeof(float) > 220 * 1024) return cudaErrorInvalidValue;
+  if (G < 1 || H % G != 0 || V > 512 || (size_t)(8 * D + kTile * (D + 4) + kTile * V) * sizeof(float) > 220 * 1024) return cudaErrorInvalidValue;
   SinkAttnArgs a{q, kpool, vpool, sink, block_tables, max_blocks, positions, cu, B, H, G, D, V, page, block, window, scale, out_mult, out, ld_out,
                  nsplit, chunk, part};
   const int npl = (V + 31) / 32;
-#define SINK_CASE(N) AT_DISPATCH(f32, return (sink_attention_t<AT, N>(a, T, s)))
+  if (V % 128 == 0 && D % (f32 ? 4 : 8) == 0) {            // 16-byte path: whole chunks of keys, four adjacent value columns per lane
+#define SINK_VEC(N) AT_DISPATCH(f32, return (sink_attention_t<AT, N, true>(a, T, s)))
+    if (npl <= 4) SINK_VEC(4);
+    if (npl <= 8) SINK_VEC(8);
+    SINK_VEC(16);
+#undef SINK_VEC
+  }
+#define SINK_CASE(N) AT_DISPATCH(f32, return (sink_attention_t<AT, N, false>(a, T, s)))
   if (npl <= 1) SINK_CASE(1);
   if (npl <= 2) SINK_CASE(2);
   if (npl <= 4) SINK_CASE(4);

@@ -424,6 +424,24 @@ def test_tensor_core_sizes(dtype, tol):
     close(decode_after(model, t, 40), oracle.forward(cfgd, sd, t), tol)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 6e-2)])
+def test_wide_values_long_context(dtype, tol):
+    """Value widths of 128 and 256 (the attention kernel's 16-byte path, one and two register groups per lane) over spans long enough
+    that the keys of a decoded token are split over CTAs and merged with the sink; portions of 2 to 31 tokens run the same kernel on
+    many rows; a page of 16 (a tile of 32 keys spans two pages) and of 64."""
+    cfgd = make_cfg([par(4, 2, 16, 128, 0, 8, 0.25, 24, None), par(2, 1, 8, 256, 288, 4, 0.35, 8, None), delta(2, 1, 32, 128, 4, None)], width=64, dtype=dtype)
+    model, sd = make_model(cfgd, "cuda", dtype)
+    t = toks(300, seed=13)
+    want = oracle.forward(cfgd, sd, t)
+    for pages, page_size in ((21, 16), (7, 64)):
+        s, at, got = session(model, pages=pages, page_size=page_size), 0, []
+        for n in [256, 2, 31, 5] + [1] * 6:
+            got.append(s.step([dict(id="r", tokens=t[at:at + n], want=list(range(n)))]))
+            at += n
+        close(torch.cat(got), want, tol * (3 if dtype == torch.bfloat16 else 1))
+
+
 @pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
 def test_greedy_generation_through_engine(device, dtype, tol):
     """The engine's scheduler, sampler and (on the GPU) captured decode graphs: two requests of unequal length, greedy tokens equal
