@@ -103,6 +103,40 @@ struct DeltaArgs {
   float q_scale, unit_eps;
 };
 
+// Operands of `nt` tokens (rows t0 ..) of head h for a delta-rule CTA: kq[jj] = [k unit | q unit * q_scale | decay], vs[jj] = the CTA's
+// PB value columns, bs[jj] = sigmoid(beta).  All threads load element-wise (independent loads), then one warp per token takes the two
+// sums of squares from shared memory and rescales.  Ends with a barrier.
+template <typename AT>
+__device__ __forceinline__ void delta_stage(const DeltaArgs& a, long long t0, int nt, int h, int g, int p0, int PB, float negA, float* kq, float* vs,
+                                            float* bs) {
+  const int N = a.N, GN = a.G * N, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const AT* in = reinterpret_cast<const AT*>(a.in);
+#pragma unroll 4
+  for (int e = threadIdx.x; e < nt * N; e += blockDim.x) {
+    const int jj = e / N, n = e - jj * N;
+    const AT* row = in + (t0 + jj) * a.ld_in;
+    float* dst = kq + jj * 3 * N;
+    dst[n] = ldf<AT>(row + GN + g * N + n);
+    dst[N + n] = ldf<AT>(row + g * N + n);
+    dst[2 * N + n] = expf(negA * softplus_f(a.dt[(t0 + jj) * a.ld_dt + h * N + n] + a.dt_bias[h * N + n]));
+  }
+#pragma unroll 2
+  for (int e = threadIdx.x; e < nt * PB; e += blockDim.x) {
+    const int jj = e / PB, c = e - jj * PB;
+    vs[e] = ldf<AT>(in + (t0 + jj) * a.ld_in + 2 * GN + h * a.P + p0 + c);
+  }
+  if (threadIdx.x < nt) bs[threadIdx.x] = sigmoid_f(ldf<AT>((const AT*)a.beta + (t0 + threadIdx.x) * a.ld_b + h));
+  __syncthreads();
+  for (int jj = warp; jj < nt; jj += nw) {
+    float* dst = kq + jj * 3 * N;
+    float sk = 0.f, sq = 0.f;
+    for (int n = lane; n < N; n += 32) { sk += dst[n] * dst[n]; sq += dst[N + n] * dst[N + n]; }
+    const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
+    for (int n = lane; n < N; n += 32) { dst[n] *= ik; dst[N + n] *= iq; }
+  }
+  __syncthreads();
+}
+
 constexpr int kDeltaTokensMax = 16;
 
 // One CTA per (sequence, head, block of PB value columns): the columns of S evolve independently.  S[N][PB] in shared memory; thread
@@ -140,23 +174,7 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
   for (int j0 = 0; j0 < q; j0 += kTok) {
     const int nt = min(kTok, q - j0);
     __syncthreads();                        // the last block's operands are no longer read (and the state is loaded)
-    for (int jj = warp; jj < nt; jj += nw) {
-      const long long t = s + j0 + jj;
-      const AT* row = in + t * a.ld_in;
-      float* dst = kq + jj * 3 * N;
-      float sk = 0.f, sq = 0.f;
-      for (int n = lane; n < N; n += 32) {
-        const float qv = ldf<AT>(row + g * N + n), kv = ldf<AT>(row + GN + g * N + n);
-        dst[n] = kv; dst[N + n] = qv;
-        sk += kv * kv; sq += qv * qv;
-        dst[2 * N + n] = expf(negA * softplus_f(a.dt[t * a.ld_dt + h * N + n] + a.dt_bias[h * N + n]));
-      }
-      const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
-      for (int n = lane; n < N; n += 32) { dst[n] *= ik; dst[N + n] *= iq; }     // each lane rescales what it wrote
-      for (int c = lane; c < PB; c += 32) vs[jj * PB + c] = ldf<AT>(row + 2 * GN + h * P + p0 + c);
-      if (lane == 0) bs[jj] = sigmoid_f(ldf<AT>((const AT*)a.beta + t * a.ld_b + h));
-    }
-    __syncthreads();
+    delta_stage<AT>(a, s + j0, nt, h, g, p0, PB, negA, kq, vs, bs);
     for (int jj = 0; jj < nt; ++jj) {
       const float* kr = kq + jj * 3 * N;
       if (r < R) {
@@ -198,6 +216,87 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
   } else {
     for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = S[e]; }
   }
+}
+
+// The same recurrence with the state in REGISTERS: one warp owns CW value columns, lane r holds rows n = r, r + 32, .. of each (dim <= 32
+// NRMAX), so both products S^T k and S^T q are warp reductions and a token needs no block barrier; k, q, g of a block of tokens are
+// staged in shared memory for all warps as above; NR = rows per lane (1, 2, 4 or 8).  The state block passes through a padded shared-memory tile on its way in and out so
+// that global accesses stay coalesced.                                  grid (B, H, P / PB), PB = warps * CW, block 32 * warps
+constexpr int kDeltaRowsMax = 8;
+constexpr int kDeltaWarpMinTokens = 8;      // shorter steps are bound by the state copies: the shared-memory kernel with 16-byte copies runs
+
+template <typename AT, int CW, int NR>
+__global__ void delta_scan_warp_kernel(DeltaArgs a, int kTok) {
+  extern __shared__ __align__(16) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, PB = nw * CW;
+  const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, p0 = blockIdx.z * PB;
+  const int g = h / (H / a.G), ldt = PB + 1;
+  float* tile = smem;                       // [N][PB + 1]
+  float* kq = tile + N * ldt;               // [tokens][3N]   k | q | g
+  float* vs = kq + kTok * 3 * N;            // [tokens][PB]
+  float* bs = vs + kTok * PB;               // [tokens]
+  const int s = a.cu[b], q = a.cu[b + 1] - s;
+  if (q == 0) return;
+  const bool fresh = a.ctx[b] - q == 0;
+  float* gS = a.state + ((long long)a.slots[b] * H + h) * N * P;
+  float st[CW][NR];
+  if (!fresh) {
+    for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; tile[n * ldt + c] = gS[n * P + p0 + c]; }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < CW; ++j)
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int n = lane + 32 * i;
+      st[j][i] = (!fresh && n < N) ? tile[n * ldt + warp * CW + j] : 0.f;
+    }
+  const AT* in = reinterpret_cast<const AT*>(a.in);
+  const float negA = -expf(a.A_log[h]);
+  const int GN = a.G * N;
+  for (int j0 = 0; j0 < q; j0 += kTok) {
+    const int nt = min(kTok, q - j0);
+    __syncthreads();                        // the last block's operands are no longer read
+    delta_stage<AT>(a, s + j0, nt, h, g, p0, PB, negA, kq, vs, bs);
+    for (int jj = 0; jj < nt; ++jj) {
+      const float* kr = kq + jj * 3 * N;
+      float kk[NR], qq[NR], a1[CW], a2[CW];
+#pragma unroll
+      for (int j = 0; j < CW; ++j) a1[j] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int n = lane + 32 * i;
+        const bool in_n = n < N;
+        kk[i] = in_n ? kr[n] : 0.f; qq[i] = in_n ? kr[N + n] : 0.f;
+        const float gg = in_n ? kr[2 * N + n] : 0.f;
+#pragma unroll
+        for (int j = 0; j < CW; ++j) { st[j][i] *= gg; a1[j] += st[j][i] * kk[i]; }
+      }
+      const float beta = bs[jj];
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        const float u = beta * (vs[jj * PB + warp * CW + j] - warp_sum(a1[j]));
+        a2[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) { st[j][i] += kk[i] * u; a2[j] += st[j][i] * qq[i]; }
+      }
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        const float y = warp_sum(a2[j]);
+        if (lane == j) a.out[(long long)(s + j0 + jj) * H * P + h * P + p0 + warp * CW + j] = y;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < CW; ++j)
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int n = lane + 32 * i;
+      if (n < N) tile[n * ldt + warp * CW + j] = st[j][i];
+    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = tile[n * ldt + c]; }
 }
 
 // ---------------------------------------------------------------------------------------------------------- minGRU
@@ -541,6 +640,34 @@ cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta,
                               const float* dt_bias, const float* A_log, float* state, const int* cu, const int* ctx, const int* slots, float* out,
                               int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, cudaStream_t s) {
   if (G < 1 || H % G != 0 || P < 1 || N < 1) return cudaErrorInvalidValue;
+  DeltaArgs a{in, ld_in, beta, ld_b, dt, ld_dt, dt_bias, A_log, state, cu, ctx, slots, out, H, G, N, P, q_scale, unit_eps};
+  if (N <= 32 * kDeltaRowsMax && max_q >= kDeltaWarpMinTokens) {
+    // register form: the largest column block out of 32 (8 warps x 4), 16, 8, 4, 2, 1 that divides the value width and still gives the
+    // grid two CTAs per SM (a token's latency does not depend on the block's width, so small grids take narrow blocks)
+    static const int kWarps[6] = {8, 8, 8, 4, 2, 1}, kCols[6] = {4, 2, 1, 1, 1, 1};
+    int pick = -1;
+    for (int i = 0; i < 6; ++i) {
+      const int PB = kWarps[i] * kCols[i];
+      if (P % PB != 0) continue;
+      pick = i;
+      if ((long long)B * H * (P / PB) >= 296 || PB <= 8) break;
+    }
+    const int nwarps = kWarps[pick], cw = kCols[pick], PB = nwarps * cw;
+    int stage = max_q < 1 ? 1 : (max_q < kDeltaTokensMax ? max_q : kDeltaTokensMax);
+    const size_t smem = ((size_t)N * (PB + 1) + (size_t)stage * (3 * N + PB + 1)) * sizeof(float);
+    auto go = [&](auto k) -> cudaError_t {
+      if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+      k<<<dim3(B, H, P / PB), 32 * nwarps, smem, s>>>(a, stage);
+      return last();
+    };
+    const int nr = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : 8;
+#define DELTA_CASE(C, R) if (cw == C && nr == R) { AT_DISPATCH(f32, return go(delta_scan_warp_kernel<AT, C, R>)); }
+    DELTA_CASE(4, 1) DELTA_CASE(4, 2) DELTA_CASE(4, 4) DELTA_CASE(4, 8)
+    DELTA_CASE(2, 1) DELTA_CASE(2, 2) DELTA_CASE(2, 4) DELTA_CASE(2, 8)
+    DELTA_CASE(1, 1) DELTA_CASE(1, 2) DELTA_CASE(1, 4) DELTA_CASE(1, 8)
+#undef DELTA_CASE
+    return cudaErrorInvalidValue;
+  }
   // columns of the state are independent: split a head's value dimension over CTAs (PB columns each) while the grid is small
   int PB = P;
   while (PB > 16 && PB % 2 == 0 && ((long long)B * H * (P / PB) < 592 || PB > 256)) PB /= 2;
@@ -554,7 +681,6 @@ cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta,
   while (stage > 1 && bytes(stage) > 200 * 1024) stage /= 2;
   const size_t smem = bytes(stage);
   if (smem > 220 * 1024) return cudaErrorInvalidValue;
-  DeltaArgs a{in, ld_in, beta, ld_b, dt, ld_dt, dt_bias, A_log, state, cu, ctx, slots, out, H, G, N, P, q_scale, unit_eps};
   if (f32) {
     auto k = delta_scan_kernel<float>;
     if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
