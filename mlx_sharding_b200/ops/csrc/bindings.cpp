@@ -1244,10 +1244,12 @@ Tensor hy_delta_scan(const Tensor& qkv, const Tensor& beta, const Tensor& dt, co
   const c10::cuda::CUDAGuard guard(qkv.device());
   Tensor out = torch::empty({qkv.size(0), H * V}, qkv.options().dtype(torch::kFloat32));
   if (qkv.size(0) == 0) return out;
+  Tensor pre;
+  if (b200::delta_scan_wants_prepare((int)Dk, (int)max_q)) { pre = torch::empty({qkv.size(0), (int64_t)b200::delta_scan_prepare_width((int)G, (int)H, (int)Dk, (int)V)}, out.options()); ++g_launches; }
   LAUNCH_OK(b200::delta_scan_launch(qkv.data_ptr(), qkv.stride(0), beta.data_ptr(), beta.stride(0), dt.data_ptr<float>(), dt.stride(0), dt_bias.data_ptr<float>(),
                                     A_log.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(), ctx.data_ptr<int>(), slots.data_ptr<int>(),
                                     out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)G, (int)Dk, (int)V, (float)q_scale, (float)unit_eps, is_f32(qkv),
-                                    (int)max_q, cur_stream()));
+                                    (int)max_q, pre.defined() ? pre.data_ptr<float>() : nullptr, (int)qkv.size(0), cur_stream()));
   return out;
 }
 

@@ -101,41 +101,85 @@ struct DeltaArgs {
   float* out;                               // fp32 [T, H*P]
   int H, G, N, P;
   float q_scale, unit_eps;
+  const float* pre; long long ld_pre;       // register form only: fp32 rows [k unit | q unit * q_scale | decay | v | sigmoid(beta)] (delta_prepare_kernel)
 };
 
-// Operands of `nt` tokens (rows t0 ..) of head h for a delta-rule CTA: kq[jj] = [k unit | q unit * q_scale | decay], vs[jj] = the CTA's
-// PB value columns, bs[jj] = sigmoid(beta).  All threads load element-wise (independent loads), then one warp per token takes the two
-// sums of squares from shared memory and rescales.  Ends with a barrier.
+// Operands of `nt` tokens (rows t0 ..) of head h for a delta-rule CTA: kq[jj] = [k unit | q unit * q_scale | decay], each `ldn` >= N
+// floats wide (zeros behind N), vs[jj] = the CTA's PB value columns (zeros behind the head's last column), bs[jj] = sigmoid(beta).
+// All threads load element-wise (independent loads), then one warp per token takes the two sums of squares from shared memory and
+// rescales.  Ends with a barrier.
 template <typename AT>
 __device__ __forceinline__ void delta_stage(const DeltaArgs& a, long long t0, int nt, int h, int g, int p0, int PB, float negA, float* kq, float* vs,
-                                            float* bs) {
+                                            float* bs, int ldn) {
   const int N = a.N, GN = a.G * N, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const AT* in = reinterpret_cast<const AT*>(a.in);
 #pragma unroll 4
-  for (int e = threadIdx.x; e < nt * N; e += blockDim.x) {
-    const int jj = e / N, n = e - jj * N;
-    const AT* row = in + (t0 + jj) * a.ld_in;
-    float* dst = kq + jj * 3 * N;
-    dst[n] = ldf<AT>(row + GN + g * N + n);
-    dst[N + n] = ldf<AT>(row + g * N + n);
-    dst[2 * N + n] = expf(negA * softplus_f(a.dt[(t0 + jj) * a.ld_dt + h * N + n] + a.dt_bias[h * N + n]));
+  for (int e = threadIdx.x; e < nt * ldn; e += blockDim.x) {
+    const int jj = e / ldn, n = e - jj * ldn;
+    float* dst = kq + jj * 3 * ldn;
+    float kv = 0.f, qv = 0.f, gv = 0.f;
+    if (n < N) {
+      const AT* row = in + (t0 + jj) * a.ld_in;
+      kv = ldf<AT>(row + GN + g * N + n);
+      qv = ldf<AT>(row + g * N + n);
+      gv = expf(negA * softplus_f(a.dt[(t0 + jj) * a.ld_dt + h * N + n] + a.dt_bias[h * N + n]));
+    }
+    dst[n] = kv; dst[ldn + n] = qv; dst[2 * ldn + n] = gv;
   }
 #pragma unroll 2
   for (int e = threadIdx.x; e < nt * PB; e += blockDim.x) {
     const int jj = e / PB, c = e - jj * PB;
-    vs[e] = ldf<AT>(in + (t0 + jj) * a.ld_in + 2 * GN + h * a.P + p0 + c);
+    vs[e] = p0 + c < a.P ? ldf<AT>(in + (t0 + jj) * a.ld_in + 2 * GN + h * a.P + p0 + c) : 0.f;
   }
   if (threadIdx.x < nt) bs[threadIdx.x] = sigmoid_f(ldf<AT>((const AT*)a.beta + (t0 + threadIdx.x) * a.ld_b + h));
   __syncthreads();
   for (int jj = warp; jj < nt; jj += nw) {
-    float* dst = kq + jj * 3 * N;
+    float* dst = kq + jj * 3 * ldn;
     float sk = 0.f, sq = 0.f;
-    for (int n = lane; n < N; n += 32) { sk += dst[n] * dst[n]; sq += dst[N + n] * dst[N + n]; }
+    for (int n = lane; n < N; n += 32) { sk += dst[n] * dst[n]; sq += dst[ldn + n] * dst[ldn + n]; }
     const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
-    for (int n = lane; n < N; n += 32) { dst[n] *= ik; dst[N + n] *= iq; }
+    for (int n = lane; n < N; n += 32) { dst[n] *= ik; dst[ldn + n] *= iq; }
   }
   __syncthreads();
 }
+
+// The token-wise part of the delta rule's operands, once per step instead of once per column block, as fp32 rows
+// [k unit: G N | q unit * q_scale: G N | decay: H N | v: H P | sigmoid(beta): H] (row stride ld_pre, a multiple of 4 floats), so that
+// the scan can fetch them with asynchronous copies.                                                          grid (T), block 256
+__host__ __device__ inline long long delta_pre_width(int G, int H, int N, int P) { return ((long long)(2 * G + H) * N + (long long)H * P + H + 3) / 4 * 4; }
+
+template <typename AT>
+__global__ void delta_prepare_kernel(DeltaArgs a, float* __restrict__ pre) {
+  const long long t = blockIdx.x;
+  const int N = a.N, GN = a.G * N, HN = a.H * N, HP = a.H * a.P, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const AT* row = reinterpret_cast<const AT*>(a.in) + t * a.ld_in;
+  float* out = pre + t * a.ld_pre;
+  for (int gi = warp; gi < a.G; gi += nw) {
+    float sk = 0.f, sq = 0.f;
+    for (int n = lane; n < N; n += 32) {
+      const float qv = ldf<AT>(row + gi * N + n), kv = ldf<AT>(row + GN + gi * N + n);
+      sk += kv * kv; sq += qv * qv;
+    }
+    const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
+    for (int n = lane; n < N; n += 32) {
+      out[gi * N + n] = ldf<AT>(row + GN + gi * N + n) * ik;
+      out[GN + gi * N + n] = ldf<AT>(row + gi * N + n) * iq;
+    }
+  }
+  for (int e = threadIdx.x; e < HN; e += blockDim.x)
+    out[2 * GN + e] = expf(-expf(a.A_log[e / N]) * softplus_f(a.dt[t * a.ld_dt + e] + a.dt_bias[e]));
+  for (int e = threadIdx.x; e < HP; e += blockDim.x) out[2 * GN + HN + e] = ldf<AT>(row + 2 * GN + e);
+  for (int e = threadIdx.x; e < a.H; e += blockDim.x) out[2 * GN + HN + HP + e] = sigmoid_f(ldf<AT>((const AT*)a.beta + t * a.ld_b + e));
+}
+
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int kDeltaTokensMax = 16;
 
@@ -174,7 +218,7 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
   for (int j0 = 0; j0 < q; j0 += kTok) {
     const int nt = min(kTok, q - j0);
     __syncthreads();                        // the last block's operands are no longer read (and the state is loaded)
-    delta_stage<AT>(a, s + j0, nt, h, g, p0, PB, negA, kq, vs, bs);
+    delta_stage<AT>(a, s + j0, nt, h, g, p0, PB, negA, kq, vs, bs, N);
     for (int jj = 0; jj < nt; ++jj) {
       const float* kr = kq + jj * 3 * N;
       if (r < R) {
@@ -218,85 +262,102 @@ __global__ void delta_scan_kernel(DeltaArgs a, int PB, int R, int kTok) {
   }
 }
 
-// The same recurrence with the state in REGISTERS: one warp owns CW value columns, lane r holds rows n = r, r + 32, .. of each (dim <= 32
-// NRMAX), so both products S^T k and S^T q are warp reductions and a token needs no block barrier; k, q, g of a block of tokens are
-// staged in shared memory for all warps as above; NR = rows per lane (1, 2, 4 or 8).  The state block passes through a padded shared-memory tile on its way in and out so
-// that global accesses stay coalesced.                                  grid (B, H, P / PB), PB = warps * CW, block 32 * warps
-constexpr int kDeltaRowsMax = 8;
+// The same recurrence with the state in REGISTERS, for portions of many tokens (bound by the latency of a token, not by the state's
+// bytes): L lanes share a value column, lane l holding the key rows 4 (l + L j) + e (j < NR4, e < 4: 16-byte shared-memory loads of k, q
+// and the decay, consecutive over the lanes), so a warp runs 32 / L columns at once, both products S^T k and S^T q end in log2(L)
+// shuffles, and a token needs no block barrier.  The operands of 16 tokens at a time come from delta_prepare_kernel's rows by asynchronous
+// copies into one of two buffers while the block before is computed (rows padded with zeros to 4 L NR4, so the token loop has no
+// bounds checks).                                                                grid (B, H, ceil(P / PB)), PB = warps * 32 / L
 constexpr int kDeltaWarpMinTokens = 8;      // shorter steps are bound by the state copies: the shared-memory kernel with 16-byte copies runs
 
-template <typename AT, int CW, int NR>
+template <typename AT, int L, int NR4>
 __global__ void delta_scan_warp_kernel(DeltaArgs a, int kTok) {
+  constexpr int CPW = 32 / L, NP = 4 * L * NR4;
   extern __shared__ __align__(16) float smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, PB = nw * CW;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, PB = nw * CPW;
+  const int l = lane % L, cw = lane / L;
   const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, p0 = blockIdx.z * PB;
-  const int g = h / (H / a.G), ldt = PB + 1;
-  float* tile = smem;                       // [N][PB + 1]
-  float* kq = tile + N * ldt;               // [tokens][3N]   k | q | g
-  float* vs = kq + kTok * 3 * N;            // [tokens][PB]
-  float* bs = vs + kTok * PB;               // [tokens]
+  const int g = h / (H / a.G), col = warp * CPW + cw, pc = p0 + col;
+  const bool colok = pc < P;
+  const int per = 3 * NP + PB + 4;          // floats of one token: k | q | g | v | beta (padded to 16 bytes)
   const int s = a.cu[b], q = a.cu[b + 1] - s;
   if (q == 0) return;
   const bool fresh = a.ctx[b] - q == 0;
   float* gS = a.state + ((long long)a.slots[b] * H + h) * N * P;
-  float st[CW][NR];
-  if (!fresh) {
-    for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; tile[n * ldt + c] = gS[n * P + p0 + c]; }
-    __syncthreads();
-  }
+  float st[4 * NR4];
 #pragma unroll
-  for (int j = 0; j < CW; ++j)
+  for (int j = 0; j < NR4; ++j)
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int n = lane + 32 * i;
-      st[j][i] = (!fresh && n < N) ? tile[n * ldt + warp * CW + j] : 0.f;
+    for (int e = 0; e < 4; ++e) {
+      const int n = 4 * (l + L * j) + e;
+      st[4 * j + e] = (!fresh && colok && n < N) ? gS[(long long)n * P + pc] : 0.f;
     }
-  const AT* in = reinterpret_cast<const AT*>(a.in);
-  const float negA = -expf(a.A_log[h]);
-  const int GN = a.G * N;
-  for (int j0 = 0; j0 < q; j0 += kTok) {
+  // both staging buffers start as zeros: rows behind N and columns behind P are never copied
+  for (int e = threadIdx.x; e < 2 * kTok * per; e += blockDim.x) smem[e] = 0.f;
+  __syncthreads();
+  const int GN = a.G * N, HN = H * N, vw = min(PB, P - p0);
+  const bool vec = N % 4 == 0 && P % 4 == 0 && PB % 4 == 0;          // 16-byte copies: every segment starts and ends on a 16-byte boundary
+  const int n4 = vec ? N / 4 : N, v4 = vec ? vw / 4 : vw, items = 3 * n4 + v4 + 1;
+  // asynchronous copies of the operands of tokens t0 .. t0 + nt into buffer `buf`: all of a block are in flight at once
+  auto fetch = [&](long long t0, int nt, float* buf) {
+    for (int e = threadIdx.x; e < nt * items; e += blockDim.x) {
+      const int jj = e / items, c = e - jj * items;
+      const float* pr = a.pre + (t0 + jj) * a.ld_pre;
+      float* dst = buf + jj * per;
+      if (c >= 3 * n4 + v4) { cp_async_4(dst + 3 * NP + PB, pr + 2 * GN + HN + H * P + h); continue; }
+      const int seg = c < 3 * n4 ? c / n4 : 3, i = c - seg * n4;
+      const float* src = seg == 0 ? pr + g * N : seg == 1 ? pr + GN + g * N : seg == 2 ? pr + 2 * GN + h * N : pr + 2 * GN + HN + h * P + p0;
+      float* d = seg == 3 ? dst + 3 * NP : dst + seg * NP;
+      if (vec) cp_async_16(d + 4 * i, src + 4 * i); else cp_async_4(d + i, src + i);
+    }
+    cp_async_commit();
+  };
+  fetch(s, min(kTok, q), smem);
+  int blk = 0;
+  for (int j0 = 0; j0 < q; j0 += kTok, ++blk) {
     const int nt = min(kTok, q - j0);
-    __syncthreads();                        // the last block's operands are no longer read
-    delta_stage<AT>(a, s + j0, nt, h, g, p0, PB, negA, kq, vs, bs);
+    cp_async_wait_all();
+    __syncthreads();                        // this block's operands have landed for every thread; the other buffer is no longer read
+    if (j0 + kTok < q) fetch(s + j0 + kTok, min(kTok, q - j0 - kTok), smem + ((blk + 1) & 1) * kTok * per);
+    const float* cur = smem + (blk & 1) * kTok * per;
     for (int jj = 0; jj < nt; ++jj) {
-      const float* kr = kq + jj * 3 * N;
-      float kk[NR], qq[NR], a1[CW], a2[CW];
+      const float* tk = cur + jj * per;
+      const float4* k4 = reinterpret_cast<const float4*>(tk) + l;
+      const float4* q4 = k4 + NP / 4;
+      const float4* g4 = k4 + 2 * (NP / 4);
+      float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < CW; ++j) a1[j] = 0.f;
-#pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const int n = lane + 32 * i;
-        const bool in_n = n < N;
-        kk[i] = in_n ? kr[n] : 0.f; qq[i] = in_n ? kr[N + n] : 0.f;
-        const float gg = in_n ? kr[2 * N + n] : 0.f;
-#pragma unroll
-        for (int j = 0; j < CW; ++j) { st[j][i] *= gg; a1[j] += st[j][i] * kk[i]; }
+      for (int j = 0; j < NR4; ++j) {
+        const float4 kk = k4[j * L], gg = g4[j * L];
+        st[4 * j] *= gg.x; st[4 * j + 1] *= gg.y; st[4 * j + 2] *= gg.z; st[4 * j + 3] *= gg.w;
+        a0 += st[4 * j] * kk.x + st[4 * j + 2] * kk.z;
+        a1 += st[4 * j + 1] * kk.y + st[4 * j + 3] * kk.w;
       }
-      const float beta = bs[jj];
+      float sk = a0 + a1;
 #pragma unroll
-      for (int j = 0; j < CW; ++j) {
-        const float u = beta * (vs[jj * PB + warp * CW + j] - warp_sum(a1[j]));
-        a2[j] = 0.f;
+      for (int o = L / 2; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      const float u = tk[3 * NP + PB] * (tk[3 * NP + col] - sk);
+      a0 = 0.f; a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < NR; ++i) { st[j][i] += kk[i] * u; a2[j] += st[j][i] * qq[i]; }
+      for (int j = 0; j < NR4; ++j) {
+        const float4 kk = k4[j * L], qq = q4[j * L];
+        st[4 * j] += kk.x * u; st[4 * j + 1] += kk.y * u; st[4 * j + 2] += kk.z * u; st[4 * j + 3] += kk.w * u;
+        a0 += st[4 * j] * qq.x + st[4 * j + 2] * qq.z;
+        a1 += st[4 * j + 1] * qq.y + st[4 * j + 3] * qq.w;
       }
+      float y = a0 + a1;
 #pragma unroll
-      for (int j = 0; j < CW; ++j) {
-        const float y = warp_sum(a2[j]);
-        if (lane == j) a.out[(long long)(s + j0 + jj) * H * P + h * P + p0 + warp * CW + j] = y;
-      }
+      for (int o = L / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (l == 0 && colok) a.out[(long long)(s + j0 + jj) * H * P + h * P + pc] = y;
     }
   }
-  __syncthreads();
 #pragma unroll
-  for (int j = 0; j < CW; ++j)
+  for (int j = 0; j < NR4; ++j)
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int n = lane + 32 * i;
-      if (n < N) tile[n * ldt + warp * CW + j] = st[j][i];
+    for (int e = 0; e < 4; ++e) {
+      const int n = 4 * (l + L * j) + e;
+      if (colok && n < N) gS[(long long)n * P + pc] = st[4 * j + e];
     }
-  __syncthreads();
-  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = tile[n * ldt + c]; }
 }
 
 // ---------------------------------------------------------------------------------------------------------- minGRU
@@ -638,33 +699,35 @@ cudaError_t relu2_launch(void* x, long long ld, int n, bool f32, int T, cudaStre
 
 cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta, long long ld_b, const float* dt, long long ld_dt,
                               const float* dt_bias, const float* A_log, float* state, const int* cu, const int* ctx, const int* slots, float* out,
-                              int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, cudaStream_t s) {
+                              int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, float* pre, int T, cudaStream_t s) {
   if (G < 1 || H % G != 0 || P < 1 || N < 1) return cudaErrorInvalidValue;
-  DeltaArgs a{in, ld_in, beta, ld_b, dt, ld_dt, dt_bias, A_log, state, cu, ctx, slots, out, H, G, N, P, q_scale, unit_eps};
-  if (N <= 32 * kDeltaRowsMax && max_q >= kDeltaWarpMinTokens) {
-    // register form: the largest column block out of 32 (8 warps x 4), 16, 8, 4, 2, 1 that divides the value width and still gives the
-    // grid two CTAs per SM (a token's latency does not depend on the block's width, so small grids take narrow blocks)
-    static const int kWarps[6] = {8, 8, 8, 4, 2, 1}, kCols[6] = {4, 2, 1, 1, 1, 1};
-    int pick = -1;
-    for (int i = 0; i < 6; ++i) {
-      const int PB = kWarps[i] * kCols[i];
-      if (P % PB != 0) continue;
-      pick = i;
-      if ((long long)B * H * (P / PB) >= 296 || PB <= 8) break;
-    }
-    const int nwarps = kWarps[pick], cw = kCols[pick], PB = nwarps * cw;
-    int stage = max_q < 1 ? 1 : (max_q < kDeltaTokensMax ? max_q : kDeltaTokensMax);
-    const size_t smem = ((size_t)N * (PB + 1) + (size_t)stage * (3 * N + PB + 1)) * sizeof(float);
+  DeltaArgs a{in, ld_in, beta, ld_b, dt, ld_dt, dt_bias, A_log, state, cu, ctx, slots, out, H, G, N, P, q_scale, unit_eps, nullptr, 0};
+  if (delta_scan_wants_prepare(N, max_q)) {
+    if (pre == nullptr) return cudaErrorInvalidValue;
+    a.pre = pre; a.ld_pre = delta_pre_width(G, H, N, P);
+    AT_DISPATCH(f32, (delta_prepare_kernel<AT><<<T, 256, 0, s>>>(a, pre)));
+    // register form: 4 lanes per value column (8 beyond 128 key rows), up to 4 warps per CTA.  A warp's time per token is its serial
+    // instruction count, so while the grid leaves SMs idle (one short batch) a column is spread over more lanes: fewer rows per lane,
+    // one more shuffle level, twice the CTAs
+    int L = N <= 128 ? 4 : 8;
+    auto ctas = [&](int lanes) { const int pb = 4 * (32 / lanes); return (long long)B * H * ((P + pb - 1) / pb); };
+    while (L < 16 && ctas(L) < 148 && N > 4 * L) L *= 2;
+    const int cpw = 32 / L;
+    const int need = (N + 4 * L - 1) / (4 * L), nr4 = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+    int nwarps = (P + cpw - 1) / cpw;
+    if (nwarps > 4) nwarps = 4;
+    const int PB = nwarps * cpw, NP = 4 * L * nr4;
+    const int stage = max_q < kDeltaTokensMax ? max_q : kDeltaTokensMax;
+    const size_t smem = 2 * (size_t)stage * (3 * NP + PB + 4) * sizeof(float);
     auto go = [&](auto k) -> cudaError_t {
       if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
-      k<<<dim3(B, H, P / PB), 32 * nwarps, smem, s>>>(a, stage);
+      k<<<dim3(B, H, (P + PB - 1) / PB), 32 * nwarps, smem, s>>>(a, stage);
       return last();
     };
-    const int nr = N <= 32 ? 1 : N <= 64 ? 2 : N <= 128 ? 4 : 8;
-#define DELTA_CASE(C, R) if (cw == C && nr == R) { AT_DISPATCH(f32, return go(delta_scan_warp_kernel<AT, C, R>)); }
+#define DELTA_CASE(LL, R) if (L == LL && nr4 == R) { AT_DISPATCH(f32, return go(delta_scan_warp_kernel<AT, LL, R>)); }
     DELTA_CASE(4, 1) DELTA_CASE(4, 2) DELTA_CASE(4, 4) DELTA_CASE(4, 8)
-    DELTA_CASE(2, 1) DELTA_CASE(2, 2) DELTA_CASE(2, 4) DELTA_CASE(2, 8)
-    DELTA_CASE(1, 1) DELTA_CASE(1, 2) DELTA_CASE(1, 4) DELTA_CASE(1, 8)
+    DELTA_CASE(8, 1) DELTA_CASE(8, 2) DELTA_CASE(8, 4) DELTA_CASE(8, 8)
+    DELTA_CASE(16, 1) DELTA_CASE(16, 2) DELTA_CASE(16, 4)
 #undef DELTA_CASE
     return cudaErrorInvalidValue;
   }
@@ -711,6 +774,9 @@ cudaError_t qk_norm_rope_append_launch(const void* rows, long long ld, int q0, i
                                                                         slot_map, page, qout, (AT*)kpool, (AT*)vpool)));
   return last();
 }
+
+bool delta_scan_wants_prepare(int N, int max_q) { return N <= 256 && max_q >= kDeltaWarpMinTokens; }
+long long delta_scan_prepare_width(int G, int H, int N, int P) { return delta_pre_width(G, H, N, P); }
 
 int sink_attention_warps(int H, int G) {
   const int rg = H / G;

@@ -14,7 +14,11 @@ cudaError_t hyper_step_launch(float* xs, const float* y, long long ld_y, const f
 cudaError_t relu2_launch(void* x, long long ld, int n, bool f32, int T, cudaStream_t s);
 cudaError_t delta_scan_launch(const void* in, long long ld_in, const void* beta, long long ld_b, const float* dt, long long ld_dt,
                               const float* dt_bias, const float* A_log, float* state, const int* cu, const int* ctx, const int* slots, float* out,
-                              int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, cudaStream_t s);
+                              int B, int H, int G, int N, int P, float q_scale, float unit_eps, bool f32, int max_q, float* pre, int T, cudaStream_t s);
+// true: the step runs the register form of the scan, which takes a workspace `pre` of T * delta_scan_prepare_width(..) floats (token-wise
+// operands, computed once per step)
+bool delta_scan_wants_prepare(int N, int max_q);
+long long delta_scan_prepare_width(int G, int H, int N, int P);
 cudaError_t mingru_scan_launch(const void* rows, long long ld, int z0, int x0, int g0, int R, float* state, const int* cu, const int* ctx,
                                const int* slots, float out_mult, void* out, long long ld_out, int B, bool f32, int max_q, cudaStream_t s);
 cudaError_t qk_norm_rope_append_launch(const void* rows, long long ld, int q0, int k0, int v0, int H, int G, int D, int V, const float* qn,
