@@ -386,6 +386,9 @@ def gokapel_kernel_table(width, dev, hbm):
         aflops = 2 * H * (D + V) * pairs
         ms = timed(lambda: O.sink_attention(qf, kp, vp, sink, meta, D ** -0.5, BLK, 0, 0.6, bf))
         add(f"sink_attention(block {BLK}) {phase}", ms, abytes, flops=aflops)
+        if phase == "prefill":
+            ms = timed(lambda: O.sink_attention_prefill(qf, kp, vp, sink, meta, D ** -0.5, BLK, 0, 0.6, bf))
+            add(f"sink_attention_prefill(GEMM form, block {BLK}) prefill", ms, abytes, flops=aflops)
         ms = timed(lambda: O.qk_norm_rope_append(u, 0, H * D, H * D + G * D, H, D, qn, qn, 1e-6, inv, kp, vp, meta))
         add(f"qk_norm_rope_append {phase}", ms, T * (H * D + G * D + G * V) * 2 + T * H * D * 4 + T * G * (D + V) * 2)
         pool = torch.randn(npg, 1, PS, Lr + R, device=dev).to(bf)
@@ -395,6 +398,10 @@ def gokapel_kernel_table(width, dev, hbm):
         lbytes = (B * seen * (Lr + R) * 2 if q == 1 else (ctx0 + q) * (Lr + R) * 2) + T * Hl * (2 * Lr + R) * 2
         ms = timed(lambda: O.latent_attention(qq, pool, None, meta, 0.07, Lr, linv, window=BLK, interleaved=True))
         add(f"latent_attention(window {BLK}) (Gusolorn) {phase}", ms, lbytes, like=f"sink_attention(block {BLK}) {phase}", flops=2 * Hl * (2 * Lr + R) * lpairs)
+        if phase == "prefill":
+            ms = timed(lambda: O.latent_attention_prefill(qq.clone(), pool, None, meta, 0.07, Lr, linv, window=BLK, interleaved=True))
+            add(f"latent_attention_prefill(GEMM form, window {BLK}) (Gusolorn) prefill", ms, lbytes, like=f"sink_attention_prefill(GEMM form, block {BLK}) prefill",
+                flops=2 * Hl * (2 * Lr + R) * lpairs)
         dq = torch.randn(T, Lr + R, device=dev).to(bf)
         ms = timed(lambda: O.latent_kv_prologue(dq, 0, Lr, None, torch.ones(Lr, device=dev), 1e-6, pool, meta, linv, interleaved=True))
         add(f"latent_kv_prologue (Gusolorn) {phase}", ms, 2 * T * (Lr + R) * 2, like=f"qk_norm_rope_append {phase}")

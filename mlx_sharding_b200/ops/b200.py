@@ -847,12 +847,14 @@ def sink_attention_prefill(q, kpool, vpool, sink, meta: BatchMeta, scale: float,
     Vc = vpool[pages].permute(1, 0, 2, 3).reshape(G, -1, V)[:, skip:]
     if Kc.shape[1] < npad:
         Kc, Vc = torch.nn.functional.pad(Kc, (0, 0, 0, npad - Kc.shape[1])), torch.nn.functional.pad(Vc, (0, 0, 0, npad - Vc.shape[1]))
-    Kc, Vt = Kc[:, :npad].contiguous(), Vc[:, :npad].transpose(1, 2).contiguous()                  # [G, npad, D], [G, V, npad]
+    Kc, Vc = Kc[:, :npad].contiguous(), Vc[:, :npad]                                               # [G, npad, D], [G, npad, V]
     if out is None:
         out, out_col0 = torch.empty(T, H * V, dtype=adt, device=q.device), 0
-    qa = q.to(adt).view(T, G, Rg, D)
+    qa = q.to(adt).view(T, G, Rg, D).transpose(0, 1).contiguous()                                  # [G, T, Rg, D]: a head group's rows are a view
     is32 = _is32(adt)
     span = block if block > 0 else ctx
+    # (the host issues every launch of this path one by one: few, large products beat many small ones, so a block's queries go in one
+    # piece unless their score matrix would pass 256 MB)
     piece = max(1, (1 << 26) // (min(npad, span + 8) * Rg))
     for bs in range(first, ctx, span):
         be = min(bs + span, ctx)
@@ -860,13 +862,14 @@ def sink_attention_prefill(q, kpool, vpool, sink, meta: BatchMeta, scale: float,
         for t0 in range(t_lo, t_hi, piece):
             n = min(t_hi, t0 + piece) - t0
             ka, kb = bs - first, min(npad, (ctx0 + t0 + n - first + 7) // 8 * 8)            # keys this piece can see, as rows of Kc
+            Vt = Vc[:, ka:kb].transpose(1, 2).contiguous()                                    # [G, V, keys] for all head groups at once
             for g in range(G):
                 sg = None if sink is None else sink[g * Rg:(g + 1) * Rg]
-                sc = linear_any(qa[t0:t0 + n, g].reshape(n * Rg, D), LinearWeight(weight=Kc[g, ka:kb]), torch.float32)
+                sc = linear_any(qa[g, t0:t0 + n].view(n * Rg, D), LinearWeight(weight=Kc[g, ka:kb]), torch.float32)
                 pr = C().hy_sink_softmax(sc, sg, int(Rg), int(ctx0 + t0), float(scale), is32, 0, int(bs), 0.0, 0.0, 1.0)
-                o = linear_any(pr, LinearWeight(weight=Vt[g, :, ka:kb].contiguous()), torch.float32)
+                o = linear_any(pr, LinearWeight(weight=Vt[g]), torch.float32)
                 c0 = out_col0 + g * Rg * V
-                out[t0:t0 + n, c0:c0 + Rg * V] = (o * out_mult).view(n, Rg * V)
+                torch.mul(o.view(n, Rg * V), out_mult, out=out[t0:t0 + n, c0:c0 + Rg * V])  # scaled and rounded to the activation type in one pass
     return out
 
 
