@@ -442,6 +442,73 @@ def test_wide_values_long_context(dtype, tol):
         close(torch.cat(got), want, tol * (3 if dtype == torch.bfloat16 else 1))
 
 
+def random_cfg(rng):
+    """A configuration drawn at random: 2 to 4 owning layers of either mixer in any order plus layers that run on their weights, every
+    size, constant and feed-forward kind drawn anew."""
+    def moe():
+        ng, keep = rng.choice([(1, 1), (2, 1), (4, 2), (3, 2), (4, 3)])
+        per = rng.choice([2, 3, 4])
+        d = dict(kind="moe", router=dict(experts=ng * per, top=rng.randint(1, min(4, keep * per)), groups=dict(count=ng, keep=keep)),
+                 expert=dict(ff=rng.choice([24, 32, 40])))
+        if rng.random() < 0.7:
+            d["shared"] = dict(ff=rng.choice([16, 24]))
+        return d
+
+    def mlp():
+        r = rng.random()
+        return None if r < 0.15 else (dict(kind="dense", ff=rng.choice([40, 72])) if r < 0.55 else moe())
+
+    def layer():
+        kv, rep = rng.choice([1, 2, 3]), rng.choice([1, 2])
+        if rng.random() < 0.5:
+            return delta(kv * rep, kv, rng.choice([8, 12, 32]), rng.choice([8, 20, 32]), rng.choice([1, 2, 3, 4]), mlp())
+        dim = rng.choice([8, 16, 32])
+        return par(kv * rep, kv, dim, rng.choice([8, 24, 128]), rng.choice([0, 5, 16, 24, 33]), rng.choice([0, dim, dim // 2, 4]), rng.choice([0.125, 0.3]),
+                   rng.choice([12, 40]), mlp(), ls=rng.choice([0.6, 1.0]), rs=rng.choice([0.5, 1.0]), base=rng.choice([10000.0, 50.0]))
+
+    base = [layer() for _ in range(rng.randint(2, 4))]
+    layers = [(j, L) for j, L in enumerate(base)] + [(j, dict(copy.deepcopy(L), weights_of=j)) for j, L in enumerate(base) if rng.random() < 0.4]
+    rng.shuffle(layers)
+    owner_at = {j: i for i, (j, L) in enumerate(layers) if "weights_of" not in L}
+    for j, L in layers:
+        if "weights_of" in L:
+            L["weights_of"] = owner_at[j]
+    return make_cfg([L for _, L in layers], width=rng.choice([40, 64, 72]), vocab=rng.choice([50, 77]), eps=rng.choice([1e-6, 1e-3]),
+                    mult=rng.choice([0.3, 0.5, 1.0]), streams=rng.choice([1, 2, 3, 4]), scale=rng.choice([1.0, 4.0]))
+
+
+@pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4])
+def test_random_configurations(seed, device, dtype, tol):
+    """Configurations drawn at random (layer order, sizes, constants, shared weights), two requests stepped in portions of random sizes
+    side by side, every position against the oracle.  Exact mode only: with this many routing decisions bf16 cannot be compared."""
+    import random
+
+    rng = random.Random(seed)
+    cfgd = random_cfg(rng)
+    model, sd = make_model(cfgd, device, dtype, seed=seed)
+    reqs = {"a": toks(rng.randint(50, 80), vocab=cfgd["vocab"], seed=seed), "b": toks(rng.randint(10, 40), vocab=cfgd["vocab"], seed=seed + 1)}
+    want = {n: oracle.forward(cfgd, sd, t) for n, t in reqs.items()}
+    s = session(model, pages=10)
+    got, at = {"a": [], "b": []}, {"a": 0, "b": 0}
+    while any(at[n] < len(reqs[n]) for n in reqs):
+        entries = []
+        for n, sizes in (("a", [1, 2, 5, 17, 33]), ("b", [1, 1, 2, 9])):
+            if at[n] < len(reqs[n]) and (n == "a" or rng.random() < 0.7):
+                k = min(len(reqs[n]) - at[n], rng.choice(sizes))
+                entries.append(dict(id=n, tokens=reqs[n][at[n]:at[n] + k], want=list(range(k))))
+        if not entries:
+            continue
+        out = s.step(entries)
+        o = 0
+        for e in entries:
+            k = len(e["tokens"])
+            got[e["id"]].append(out[o:o + k])
+            o, at[e["id"]] = o + k, at[e["id"]] + k
+    for n in reqs:
+        close(torch.cat(got[n]), want[n], tol)
+
+
 @pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
 def test_greedy_generation_through_engine(device, dtype, tol):
     """The engine's scheduler, sampler and (on the GPU) captured decode graphs: two requests of unequal length, greedy tokens equal
