@@ -478,6 +478,21 @@ def random_cfg(rng):
 
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
+def test_checkpoint_without_optional_tensors(device, dtype, tol):
+    """A checkpoint without layer scales, gated-residual matrices and sinks: the loader takes what is there (plain stream update, ordinary
+    softmax) and the fused projections have no gate segment."""
+    cfgd = make_cfg([D_GQ, P_GQ, D_ONE], dtype=dtype)
+    cfg = ModelConfig.from_dict(cfgd)
+    sd = {k: v for k, v in random_state_dict(cfg, dtype=torch.bfloat16, seed=5) if not any(x in k for x in (".ls", ".rg", ".sink"))}
+    model = build_stage(cfg, None, dtype, device).load_state({k: v.clone() for k, v in sd.items()})
+    assert "rg" not in model.layer_weights[0]["seg"] and model.layer_weights[1]["sink"] is None and model.layer_weights[0]["ls1"] is None
+    t = toks(40, seed=3)
+    want = oracle.forward(cfgd, sd, t)
+    close(run_whole(model, t), want, tol)
+    close(decode_after(model, t, 21), want, tol)
+
+
+@pytest.mark.parametrize("device,dtype,tol", DEVICES[:2])
 @pytest.mark.parametrize("seed", [1, 2, 3, 4])
 def test_random_configurations(seed, device, dtype, tol):
     """Configurations drawn at random (layer order, sizes, constants, shared weights), two requests stepped in portions of random sizes
